@@ -1,7 +1,9 @@
 """Device storage behind the cache plan of a model.
 
 Every schedule entry that owns a paged cache gets one tensor
-``[2, pages, kv_heads, page_size, head_size]`` (keys, values): a page of one
+``[2, pages, kv_heads, page_size, head_size]`` (keys, values; two tensors
+``[pages, kv_heads, page_size, size]`` where a value head is not as large as a
+key head): a page of one
 key/value head is ``page_size * head_size`` contiguous elements, which is the
 tile the attention kernels stream.  Pages of one group share their numbering
 across the layers of the group, so one block table per request serves them all
@@ -39,7 +41,14 @@ class CacheStorage:
         self.views: list[CacheView] = []
         for index, entry in enumerate(plan.entries):
             need = entry.need
-            if entry.owner == index and isinstance(need, PagedKVNeed):
+            if entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size != need.head_size:
+                # keys and values of different sizes: one tensor each
+                pages = self.pages_per_group[entry.group]
+                self._owned[index] = tuple(
+                    torch.zeros((pages, need.num_kv_heads, page_size, size), dtype=dtype, device=device)
+                    for size in (need.head_size, need.value_size)
+                )
+            elif entry.owner == index and isinstance(need, PagedKVNeed):
                 self._owned[index] = torch.zeros(
                     (2, self.pages_per_group[entry.group], need.num_kv_heads, page_size, need.head_size),
                     dtype=dtype,
@@ -66,4 +75,8 @@ class CacheStorage:
         return [t for i, t in self._owned.items() if isinstance(self.plan.entries[i].need, StateNeed)]
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self._owned.values())
+        total = 0
+        for owned in self._owned.values():
+            for t in (owned if isinstance(owned, tuple) else (owned,)):
+                total += t.numel() * t.element_size()
+        return total

@@ -9,9 +9,11 @@ from .registry import (
     load_config,
     register_architecture,
 )
+from .tepavik import TepavikConfig
 from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
 
 register_architecture(Qwen2Config)
+register_architecture(TepavikConfig)
 
 __all__ = [
     "ConfigError",
@@ -23,6 +25,7 @@ __all__ = [
     "Qwen2Config",
     "ScheduleEntry",
     "TensorSpec",
+    "TepavikConfig",
     "config_class_for",
     "config_from_dict",
     "known_architectures",

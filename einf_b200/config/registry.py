@@ -42,8 +42,10 @@ def config_class_for(name: str) -> type[ModelConfig]:
 
 def config_from_dict(data: dict[str, Any]) -> ModelConfig:
     architectures = data.get("architectures")
+    if isinstance(data.get("architecture"), str) and not architectures:
+        architectures = [data["architecture"]]     # folders that name one class as a plain string
     if not isinstance(architectures, (list, tuple)) or not architectures:
-        raise ConfigError("config.json has no 'architectures' list naming the model class")
+        raise ConfigError("config.json has no 'architectures' list (or 'architecture' string) naming the model class")
     return config_class_for(str(architectures[0])).from_dict(data)
 
 

@@ -1,6 +1,7 @@
 // Paged causal attention for any batch: prompt portions and single decoded
-// tokens alike, float or bfloat16, any head size that is a multiple of 8 up to
-// 256, any number of heads and groups, with an optional sliding window.
+// tokens alike, float or bfloat16, any head size up to 256 (16-byte loads where
+// the size allows them), any number of heads and groups, with an optional
+// sliding window, chunked mask and soft cap on the scores.
 //
 // This is the 32-bit path's attention and the fallback of the bfloat16 path for
 // sizes its tensor-core kernels do not cover.  One warp owns one (token, query
@@ -11,7 +12,10 @@
 //   output: lane d accumulates sum_j p_j V[j][d] in 32-bit
 // (reference for the maths: src/einf/executors/torch/ops/csrc/paged_attention_cuda.cu:74-147
 // and flash_attention_cuda.cu:126-195; lower-right causal mask model_runner.py:145.)
-// A token at position p of request r sees keys lo..p of r, lo = max(0, p - window + 1).
+// A token at position p of request r sees keys lo..p of r, lo = max(0, p - window + 1); with a
+// chunk size c (chunked attention) lo is also at least floor(p / c) * c, the first position of p's
+// own chunk, counted from position 0 of the sequence.  With a soft cap z the scaled score s becomes
+// z * tanh(s / z) before the softmax.  Keys and values may have different sizes per head.
 #include "common.cuh"
 
 namespace einf {
@@ -43,8 +47,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_cache, const int* __restrict__ block_table,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                T* __restrict__ out, int num_rows, int num_heads, int num_kv_heads,
-                               int head_size, int page_size, int num_pages, int table_width,
-                               float scale, int window, int* status) {
+                               int head_size, int value_size, int page_size, int num_pages, int table_width,
+                               float scale, int window, int chunk, float softcap, int* status) {
   __shared__ float q_smem[kWarpsPerBlock][kMaxHeadSize];
   pdl_launch_dependents();
   pdl_wait();
@@ -56,7 +60,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   const int kv_head = h / (num_heads / num_kv_heads);
   const int r = seq_of_token[t];
   const int pos = positions[t];
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+  const bool vectors = head_size % Vec<T>::N == 0;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int* table = block_table + (size_t)r * table_width;
 
   const T* q_row = q + (size_t)row * head_size;
@@ -74,23 +81,27 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   for (int base = lo; base <= pos; base += 32) {
     const int j = base + lane;
     float s = -INFINITY;
-    long long key_offset = -1;  // element offset of (page, kv_head, slot) row, or -1
+    long long key_row = -1;  // index of the (page, kv_head, slot) row in the caches, or -1
     if (j <= pos) {
       const int logical = j / page_size;
       const int page = table[logical];
       if (page < 0 || page >= num_pages) {
         bad_page = true;
       } else {
-        key_offset = (((long long)page * num_kv_heads + kv_head) * page_size + (j - logical * page_size)) * head_size;
-        const T* k_row = k_cache + key_offset;
+        key_row = ((long long)page * num_kv_heads + kv_head) * page_size + (j - logical * page_size);
+        const T* k_row = k_cache + key_row * head_size;
         float dot = 0.f;
-        for (int d = 0; d < head_size; d += Vec<T>::N) {
-          Vec<T> kv;
-          kv.raw = *reinterpret_cast<const decltype(kv.raw)*>(k_row + d);
+        if (vectors) {
+          for (int d = 0; d < head_size; d += Vec<T>::N) {
+            Vec<T> kv;
+            kv.raw = *reinterpret_cast<const decltype(kv.raw)*>(k_row + d);
 #pragma unroll
-          for (int e = 0; e < Vec<T>::N; ++e) dot = fmaf(qs[d + e], kv.get(e), dot);
+            for (int e = 0; e < Vec<T>::N; ++e) dot = fmaf(qs[d + e], kv.get(e), dot);
+          }
+        } else {
+          for (int d = 0; d < head_size; ++d) dot = fmaf(qs[d], to_float(k_row[d]), dot);
         }
-        s = dot;
+        s = softcap > 0.f ? softcap * tanhf(dot * inv_cap) : dot;
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -104,23 +115,23 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     const int count = min(32, pos - base + 1);
     for (int kk = 0; kk < count; ++kk) {
       const float pj = __shfl_sync(0xffffffffu, p, kk);
-      const long long off = __shfl_sync(0xffffffffu, key_offset, kk);
+      const long long off = __shfl_sync(0xffffffffu, key_row, kk);
       if (off < 0) continue;
-      const T* v_row = v_cache + off;
+      const T* v_row = v_cache + off * value_size;
 #pragma unroll
       for (int i = 0; i < kDimsPerLane; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_size) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
+        if (d < value_size) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
       }
     }
   }
   if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(status, kStatusBadPage);
   const float inv = l > 0.f ? 1.f / l : 0.f;
-  T* o_row = out + (size_t)row * head_size;
+  T* o_row = out + (size_t)row * value_size;
 #pragma unroll
   for (int i = 0; i < kDimsPerLane; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_size) o_row[d] = from_float<T>(acc[i] * inv);
+    if (d < value_size) o_row[d] = from_float<T>(acc[i] * inv);
   }
 }
 
@@ -131,17 +142,20 @@ using namespace einf;
 extern "C" int einf_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
                                             int dtype, const int* block_table, const int* seq_of_token,
                                             const int* positions, void* out, int num_tokens,
-                                            int num_heads, int num_kv_heads, int head_size,
+                                            int num_heads, int num_kv_heads, int head_size, int value_size,
                                             int page_size, int num_pages, int table_width, float scale,
-                                            int window, int* status, cudaStream_t stream) {
+                                            int window, int chunk, float softcap, int* status,
+                                            cudaStream_t stream) {
   const int rows = num_tokens * num_heads;
   if (rows == 0) return 0;
-  if (head_size > kMaxHeadSize || head_size % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (head_size > kMaxHeadSize || value_size > kMaxHeadSize || head_size <= 0 || value_size <= 0)
+    return (int)cudaErrorInvalidValue;
   const int blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   EINF_DISPATCH_2(dtype, T, {
     paged_attention_generic_kernel<T><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
-        rows, num_heads, num_kv_heads, head_size, page_size, num_pages, table_width, scale, window, status);
+        rows, num_heads, num_kv_heads, head_size, value_size, page_size, num_pages, table_width, scale, window,
+        chunk, softcap, status);
   })
   return (int)cudaGetLastError();
 }

@@ -754,6 +754,127 @@ __global__ void zero_fresh_state_kernel(Word* __restrict__ state, long long row_
     row[i] = zero;
 }
 
+// ---------------------------------------------------------------------------
+// out[t, i] = act(x[t, i]) for the feed-forwards without a gate.  kinds (ops.ACTIVATIONS):
+//   0 squared ReLU      max(z, 0)^2
+//   1 GELU, tanh form   0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   2 SiLU              z / (1 + exp(-z))
+//   3 ReLU
+// x may be the float32 partial sums of a split-K product.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float activate(float z, int kind) {
+  switch (kind) {
+    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 2: return z / (1.f + expf(-z));
+    default: return fmaxf(z, 0.f);
+  }
+}
+
+template <typename TIn, typename T>
+__global__ void activation_kernel(const TIn* __restrict__ x, int splits, size_t split_stride, T* __restrict__ out,
+                                  int kind, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride)
+    out[idx] = from_float<T>(activate(sum_splits(x + idx, splits, split_stride), kind));
+}
+
+// Dense bfloat16 rows, eight values per thread with 16-byte accesses.
+__global__ void activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int kind,
+                                         size_t vectors) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= vectors) return;
+  const uint4 raw = reinterpret_cast<const uint4*>(x)[idx];
+  const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  uint4 result;
+  __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(in[e]);
+    rp[e] = __floats2bfloat162_rn(activate(f.x, kind), activate(f.y, kind));
+  }
+  reinterpret_cast<uint4*>(out)[idx] = result;
+}
+
+// ---------------------------------------------------------------------------
+// Bias, unit-RMS queries and keys, and the cache write of an attention layer without a rotation.
+// One warp per (token, head): the row of the product is [H query heads of `key_size` | G key heads
+// of `key_size` | G value heads of `value_size`] (G = 0: a layer that reads another layer's keys and
+// values computes queries only).  With `normalise`, a query or key head x becomes
+// x / sqrt(mean(x^2) + eps), in 32-bit, before it is rounded; values pass through.  Queries go to
+// q_out [T, H, key_size], keys and values into the pages at slots[t] (negative: not written):
+// k_cache [pages, G, page, key_size], v_cache [pages, G, page, value_size].
+// ---------------------------------------------------------------------------
+template <typename TIn, typename T>
+__global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
+                                      const float* __restrict__ bias, const int* __restrict__ slots,
+                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                      int num_tokens, int num_heads, int num_kv_heads, int key_size, int value_size,
+                                      int normalise, float eps, int page_size, int num_pages, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int per_token = num_heads + 2 * num_kv_heads;
+  if (warp >= (long long)num_tokens * per_token) return;
+  const int t = (int)(warp / per_token);
+  const int item = (int)(warp - (long long)t * per_token);
+  const int width = (num_heads + num_kv_heads) * key_size + num_kv_heads * value_size;
+  int size, base;
+  T* dst;
+  bool unit = normalise != 0;
+  if (item < num_heads) {
+    size = key_size;
+    base = item * key_size;
+    dst = q_out + ((size_t)t * num_heads + item) * key_size;
+  } else {
+    const int slot = slots ? slots[t] : -1;
+    if (slot < 0) return;
+    const int page = slot / page_size, offset = slot - page * page_size;
+    if (page >= num_pages) {
+      if (lane == 0) atomicOr(status, kStatusBadPage);
+      return;
+    }
+    if (item < num_heads + num_kv_heads) {
+      const int head = item - num_heads;
+      size = key_size;
+      base = item * key_size;
+      dst = k_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * key_size;
+    } else {
+      const int head = item - num_heads - num_kv_heads;
+      size = value_size;
+      base = (num_heads + num_kv_heads) * key_size + head * value_size;
+      dst = v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * value_size;
+      unit = false;
+    }
+  }
+  constexpr int kPerLane = 8;   // head sizes up to 256
+  const TIn* row = qkv + (size_t)t * width + base;
+  float v[kPerLane];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int d = lane + 32 * i;
+    v[i] = 0.f;
+    if (d < size) {
+      v[i] = sum_splits(row + d, splits, split_stride);
+      if (bias) v[i] += bias[base + d];
+      ss += v[i] * v[i];
+    }
+  }
+  float factor = 1.f;
+  if (unit) factor = rsqrtf(warp_sum(ss) / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int d = lane + 32 * i;
+    if (d < size) dst[d] = from_float<T>(v[i] * factor);
+  }
+}
+
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
@@ -1009,6 +1130,51 @@ extern "C" int einf_zero_fresh_state(void* state, long long row_bytes, int num_s
                            num_slots, state_slots, q_start, positions);
   return (int)launch_pdl(zero_fresh_state_kernel<uint8_t>, grid, threads, 0, stream, (uint8_t*)state, row_words,
                          num_slots, state_slots, q_start, positions);
+}
+
+extern "C" int einf_activation(const void* x, int in_dtype, int splits, long long split_stride, void* out, int dtype,
+                               long long total, int kind, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
+  const int threads = 256;
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && total % 8 == 0 && ((uintptr_t)x & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0) {
+    const size_t vectors = (size_t)total >> 3;
+    const size_t blocks = (vectors + threads - 1) / threads;
+    if (blocks < (1ull << 31))
+      return (int)launch_pdl(activation_bf16x8_kernel, (int)blocks, threads, 0, stream, (const __nv_bfloat16*)x,
+                             (__nv_bfloat16*)out, kind, vectors);
+  }
+  size_t blocks = ((size_t)total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  EINF_DISPATCH_2(in_dtype, TIn, {
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(activation_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)x, splits,
+                             (size_t)split_stride, (T*)out, kind, (size_t)total);
+    })
+  })
+}
+
+extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, long long split_stride, int dtype,
+                                   const float* bias, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                                   int num_tokens, int num_heads, int num_kv_heads, int key_size, int value_size,
+                                   int normalise, float eps, int page_size, int num_pages, int* status,
+                                   cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (key_size > 256 || value_size > 256 || key_size <= 0 || (num_kv_heads > 0 && value_size <= 0))
+    return (int)cudaErrorInvalidValue;
+  const long long warps = (long long)num_tokens * (num_heads + 2 * num_kv_heads);
+  const int threads = 128;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  EINF_DISPATCH_2(in_dtype, TIn, {
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(qkv_norm_store_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)qkv, splits,
+                             (size_t)split_stride, bias, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_tokens,
+                             num_heads, num_kv_heads, key_size, value_size, normalise, eps, page_size, num_pages,
+                             status);
+    })
+  })
 }
 
 extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long rows, int n,

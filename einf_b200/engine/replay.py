@@ -34,8 +34,8 @@ class ReplayError(RuntimeError):
 
 class TraceReplayer:
     def __init__(self, model_dir: str | Path, dtype: str, max_tokens: int, block_len: int = 16,
-                 device: str = "cuda:0", max_requests: int = 8) -> None:
-        """``max_requests``: most requests one step may hold (rows of the step buffer)."""
+                 device: str = "cuda:0", max_requests: int = 4) -> None:
+        """``max_requests``: most requests that are live at a time (rows of the step buffer, state slots)."""
         pages = -(-max_tokens // block_len)
         engine_config = EngineConfig(
             dtype=dtype,
@@ -121,7 +121,8 @@ def main(argv: list[str] | None = None) -> int:
                         help="most tokens live requests hold at any time; the cache pool is made for this many")
     parser.add_argument("--block-len", type=int, default=16, help="tokens per cache page")
     parser.add_argument("--device", default="cuda:0")
-    parser.add_argument("--max-requests", type=int, default=8, help="most requests in one step")
+    parser.add_argument("--max-requests", type=int, default=4,
+                        help="most live requests (rows of a step, state slots)")
     args = parser.parse_args(argv)
     replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, args.block_len, args.device,
                              args.max_requests)

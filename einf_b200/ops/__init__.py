@@ -503,39 +503,302 @@ def paged_attention_generic(
     scale: float,
     window: Optional[int],
     status: torch.Tensor,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
 ) -> None:
     """Causal attention of every token of the batch over the pages of its request.
 
-    ``q`` and ``out`` are ``[tokens, heads, head_size]``; caches
-    ``[pages, kv_heads, page_size, head_size]``; ``block_table`` ``[requests, width]``
-    maps a request's logical page to a physical one.
+    ``q`` is ``[tokens, heads, head_size]``, ``out`` ``[tokens, heads, value_size]``; the caches
+    ``[pages, kv_heads, page_size, head_size]`` and ``[pages, kv_heads, page_size, value_size]``;
+    ``block_table`` ``[requests, width]`` maps a request's logical page to a physical one.
+    ``window``: only the last that many keys; ``chunk``: only the keys of the token's own block of
+    that many positions (blocks counted from position 0); ``softcap`` z: scores become
+    ``z * tanh(score / z)`` before the softmax.
     """
     tokens, num_heads, head_size = q.shape
     num_pages, num_kv_heads, page_size, size = k_cache.shape
-    if size != head_size or v_cache.shape != k_cache.shape:
+    value_size = v_cache.shape[3]
+    if size != head_size or v_cache.shape[:3] != k_cache.shape[:3]:
         raise ValueError("cache head size differs from q")
-    if head_size % 8 or head_size > MAX_HEAD_SIZE:
-        raise UnsupportedSize(
-            f"paged attention takes head sizes that are multiples of 8 up to {MAX_HEAD_SIZE}, got {head_size}"
-        )
+    if max(head_size, value_size) > MAX_HEAD_SIZE:
+        raise UnsupportedSize(f"paged attention takes head sizes up to {MAX_HEAD_SIZE}, got {head_size}, {value_size}")
     if num_heads % num_kv_heads:
         raise UnsupportedSize(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("q, caches and out must share one dtype")
-    if out.shape != q.shape:
-        raise ValueError("out must have q's shape")
+    if out.shape != (tokens, num_heads, value_size):
+        raise ValueError(f"out must be {(tokens, num_heads, value_size)}, got {tuple(out.shape)}")
     fn = _fn(
         "einf_paged_attention_generic",
         [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-         c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
            _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
            _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads,
-           head_size, page_size, num_pages, block_table.shape[1], float(scale),
-           int(window) if window else 0, _dev(status, "status"), _stream()),
+           head_size, value_size, page_size, num_pages, block_table.shape[1], float(scale),
+           int(window) if window else 0, int(chunk) if chunk else 0, float(softcap) if softcap else 0.0,
+           _dev(status, "status"), _stream()),
         "paged_attention_generic",
+    )
+
+
+#: activations of :func:`activation` by name
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """``out = act(x)`` elementwise (``relu2``: the square of ReLU; ``gelu_tanh``; ``silu``; ``relu``);
+    ``x`` may be float32 partial sums ``[splits, tokens, width]`` of a split-K product."""
+    tokens, width = out.shape
+    splits, stride = _maybe_split(x, tokens, width, "x")
+    if kind not in ACTIVATIONS:
+        raise ValueError(f"unknown activation {kind!r}; known: {sorted(ACTIVATIONS)}")
+    fn = _fn("einf_activation", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(
+        fn(_dev(x, "x"), _code(x), splits, stride, _dev(out, "out"), _code(out), tokens * width, ACTIVATIONS[kind],
+           _stream()),
+        "activation",
+    )
+
+
+def qkv_norm_store(
+    qkv: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    slots: Optional[torch.Tensor],
+    q_out: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    key_size: int,
+    value_size: int,
+    unit_eps: Optional[float],
+    status: torch.Tensor,
+) -> None:
+    """For an attention layer without a rotation: add the bias, divide every query and key head by
+    its root mean square (``unit_eps`` inside the root; None: leave them), write the queries to
+    ``q_out [tokens, heads, key_size]`` and keys and values into the pages at ``slots``.  A row of
+    ``qkv`` (or of its float32 split-K partial sums) is ``[heads * key_size | kv_heads * key_size |
+    kv_heads * value_size]``; ``num_kv_heads`` 0 means the row holds queries only (the layer reads
+    another layer's pages); ``slots`` None writes no keys or values.  Caches are ``[pages, kv_heads, page, key_size]`` and ``[..., value_size]``."""
+    tokens = qkv.shape[-2]
+    width = (num_heads + num_kv_heads) * key_size + num_kv_heads * value_size
+    splits, stride = _maybe_split(qkv, tokens, width, "qkv")
+    if q_out.numel() != tokens * num_heads * key_size:
+        raise ValueError("q_out must hold [tokens, heads, key_size]")
+    if max(key_size, value_size) > MAX_HEAD_SIZE:
+        raise UnsupportedSize(f"head sizes up to {MAX_HEAD_SIZE}, got {key_size}, {value_size}")
+    page_size = num_pages = 0
+    k_ptr = v_ptr = 0
+    if num_kv_heads and slots is not None:
+        if k_cache is None or v_cache is None:
+            raise ValueError("slots given without caches")
+        num_pages, kvh, page_size, size = k_cache.shape
+        if (kvh, size) != (num_kv_heads, key_size) or v_cache.shape != (num_pages, kvh, page_size, value_size):
+            raise ValueError(
+                f"caches are {tuple(k_cache.shape)} and {tuple(v_cache.shape)}, expected "
+                f"[pages, {num_kv_heads}, page, {key_size}] and [..., {value_size}]"
+            )
+        if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
+            raise TypeError("cache dtype differs from q_out")
+        k_ptr, v_ptr = _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
+    fn = _fn(
+        "einf_qkv_norm_store",
+        [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(qkv, "qkv"), _code(qkv), splits, stride, _code(q_out), _opt(bias, "bias", torch.float32),
+           _opt(slots, "slots", torch.int32) if k_ptr else 0, _dev(q_out, "q_out"), k_ptr, v_ptr, tokens,
+           num_heads, num_kv_heads, key_size, value_size, 0 if unit_eps is None else 1,
+           float(unit_eps or 0.0), page_size, num_pages, _dev(status, "status"), _stream()),
+        "qkv_norm_store",
+    )
+
+
+def _rows_of(x: torch.Tensor, name: str) -> int:
+    """Row stride of a two-dimensional view whose rows are contiguous (a slice of columns of a wider matrix)."""
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError(f"{name} must be a matrix with unit stride along its rows")
+    if not x.is_cuda:
+        raise KernelError(f"{name} is on {x.device}: the kernels run on a CUDA device only")
+    return x.stride(0)
+
+
+#: most taps of the short convolution
+MAX_CONV_TAPS = 16
+#: most rows (key size) of a recurrent state
+MAX_STATE_ROWS = 512
+
+
+def conv_silu(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    conv_state: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    q_start: torch.Tensor,
+    state_slots: torch.Tensor,
+    out: torch.Tensor,
+    dt_raw: Optional[torch.Tensor] = None,
+    dt_bias: Optional[torch.Tensor] = None,
+    a_log: Optional[torch.Tensor] = None,
+    dt_out: Optional[torch.Tensor] = None,
+    decay_out: Optional[torch.Tensor] = None,
+) -> None:
+    """Causal convolution per channel, bias and SiLU over the tokens of every request, continued
+    from and into the requests' convolution states.
+
+    ``x [tokens, channels]`` (columns of a wider matrix are fine), ``weight [channels, taps]`` with
+    the current token's tap last, ``conv_state [slots, taps - 1, channels]`` float32 (a view whose
+    slot stride may be larger): a request's last ``taps - 1`` inputs, oldest first.  ``out
+    [tokens, channels]``.  With ``dt_raw [tokens, heads]`` (columns of the same wide matrix as
+    ``x``) the launch also writes ``dt_out = softplus(dt_raw + dt_bias)`` and ``decay_out =
+    exp(-exp(a_log) * dt_out)``, both float32 ``[tokens, heads]``."""
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    if weight.shape != (channels, taps) or weight.dtype != torch.float32 or not weight.is_contiguous():
+        raise ValueError(f"conv weight must be contiguous float32 {(channels, taps)}")
+    if not 1 <= taps <= MAX_CONV_TAPS:
+        raise UnsupportedSize(f"the convolution kernel takes 1 to {MAX_CONV_TAPS} taps, not {taps}")
+    if conv_state.dtype != torch.float32 or conv_state.shape[1:] != (taps - 1, channels) or \
+            (taps > 1 and (conv_state.stride(2) != 1 or conv_state.stride(1) != channels)):
+        raise ValueError(f"conv_state must be float32 [slots, {taps - 1}, {channels}] with contiguous slots")
+    if out.shape != (tokens, channels) or out.dtype != x.dtype:
+        raise ValueError("out must have x's shape and dtype")
+    stride = _rows_of(x, "x")
+    heads, dt_ptr = 0, 0
+    if dt_raw is not None:
+        heads = dt_raw.shape[1]
+        if _rows_of(dt_raw, "dt_raw") != stride or dt_raw.dtype != x.dtype or dt_raw.shape[0] != tokens:
+            raise ValueError("dt_raw must be columns of the matrix x comes from")
+        for name, t in (("dt_bias", dt_bias), ("a_log", a_log)):
+            if t is None or t.dtype != torch.float32 or t.shape != (heads,):
+                raise ValueError(f"{name} must be float32 [{heads}]")
+        for name, t in (("dt_out", dt_out), ("decay_out", decay_out)):
+            if t is None or t.dtype != torch.float32 or t.shape != (tokens, heads) or not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous float32 {(tokens, heads)}")
+        dt_ptr = dt_raw.data_ptr()
+    fn = _fn(
+        "einf_conv_silu",
+        [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+         c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    )
+    _check(
+        fn(x.data_ptr(), _code(x), stride, _dev(weight, "weight"), _opt(bias, "bias", torch.float32),
+           conv_state.data_ptr(), conv_state.stride(0), _opt(seq_of_token, "seq_of_token", torch.int32),
+           _opt(q_start, "q_start", torch.int32), _opt(state_slots, "state_slots", torch.int32), conv_state.shape[0],
+           state_slots.shape[0], _dev(out, "out"), channels, taps, tokens, dt_ptr,
+           _opt(dt_bias, "dt_bias", torch.float32), _opt(a_log, "a_log", torch.float32),
+           0 if dt_out is None else dt_out.data_ptr(), 0 if decay_out is None else decay_out.data_ptr(), heads,
+           _stream()),
+        "conv_silu",
+    )
+
+
+def linear_recurrence(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    state: torch.Tensor,
+    q_start: torch.Tensor,
+    state_slots: torch.Tensor,
+    y: torch.Tensor,
+    heads: int,
+    groups: int,
+    dim: int,
+    vdim: int,
+    head_decay: Optional[torch.Tensor] = None,
+    token_decay: Optional[torch.Tensor] = None,
+    token_scale: Optional[torch.Tensor] = None,
+    skip: Optional[torch.Tensor] = None,
+    silu_inputs: bool = False,
+) -> None:
+    """Per request and head, over its tokens in order, with a float32 state ``S [dim, vdim]``::
+
+        S <- a_t S + k_t (s_t v_t)^T        y_t = S^T q_t + skip_h v_t
+
+    ``q``, ``k`` are ``[tokens, groups * dim]``, ``v`` ``[tokens, heads * vdim]`` (columns of wider
+    matrices are fine); head ``h`` reads group ``h // (heads // groups)``.  ``a_t`` is
+    ``head_decay [heads]`` or ``token_decay [tokens, heads]``; ``s_t`` is ``token_scale [tokens,
+    heads]`` or 1; ``skip [heads]`` or 0; all float32.  ``silu_inputs``: q, k and v pass SiLU as
+    they are read.  ``state [slots, heads, dim, vdim]`` float32 (slot stride may be larger) is read
+    at the start of each request's portion and written at its end; ``y [tokens, heads * vdim]``
+    float32."""
+    tokens = v.shape[0]
+    if q.shape != (tokens, groups * dim) or k.shape != q.shape or v.shape != (tokens, heads * vdim):
+        raise ValueError(f"q, k must be [{tokens}, {groups * dim}] and v [{tokens}, {heads * vdim}]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k and v must share one dtype")
+    if heads % groups:
+        raise UnsupportedSize(f"{heads} heads are not a multiple of {groups} groups")
+    if dim > MAX_STATE_ROWS:
+        raise UnsupportedSize(f"the recurrence kernel takes states of up to {MAX_STATE_ROWS} rows, not {dim}")
+    if state.dtype != torch.float32 or state.shape[1:] != (heads, dim, vdim) or \
+            state[0].stride() != (dim * vdim, vdim, 1):
+        raise ValueError(f"state must be float32 [slots, {heads}, {dim}, {vdim}] with contiguous slots")
+    if y.dtype != torch.float32 or y.shape != (tokens, heads * vdim) or not y.is_contiguous():
+        raise ValueError(f"y must be contiguous float32 {(tokens, heads * vdim)}")
+    if (head_decay is None) == (token_decay is None):
+        raise ValueError("give head_decay or token_decay")
+    for name, t, shape in (("head_decay", head_decay, (heads,)), ("token_decay", token_decay, (tokens, heads)),
+                           ("token_scale", token_scale, (tokens, heads)), ("skip", skip, (heads,))):
+        if t is not None and (t.dtype != torch.float32 or t.shape != shape or not t.is_contiguous()):
+            raise ValueError(f"{name} must be contiguous float32 {shape}")
+    fn = _fn(
+        "einf_linear_recurrence",
+        [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+         c_int, c_void_p],
+    )
+    _check(
+        fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), _code(q), _rows_of(q, "q"), _rows_of(k, "k"), _rows_of(v, "v"),
+           _opt(head_decay, "head_decay", torch.float32), _opt(token_decay, "token_decay", torch.float32),
+           _opt(token_scale, "token_scale", torch.float32), _opt(skip, "skip", torch.float32),
+           state.data_ptr(), state.stride(0), state.shape[0], _opt(q_start, "q_start", torch.int32),
+           _opt(state_slots, "state_slots", torch.int32), state_slots.shape[0], _dev(y, "y"), heads, groups, dim,
+           vdim, 1 if silu_inputs else 0, _stream()),
+        "linear_recurrence",
+    )
+
+
+def gated_norm(
+    y: torch.Tensor,
+    gate: torch.Tensor,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    parts: int,
+    eps: float,
+    gate_first: bool,
+    gate_kind: str,
+) -> None:
+    """The gate and RMS norm behind a recurrence, in 32-bit: ``y [tokens, width]`` float32 is cut
+    into ``parts`` equal parts, each divided by its own root mean square.  ``gate_first``: ``u = y *
+    g(gate)``, ``out = u / rms(u) * weight``; otherwise ``out = y / rms(y) * weight * g(gate)``.
+    ``g`` is ``"silu"`` or ``"sigmoid"``; ``gate [tokens, width]`` may be columns of a wider matrix."""
+    tokens, width = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous():
+        raise TypeError("y must be contiguous float32")
+    if gate.shape != (tokens, width) or out.shape != (tokens, width) or gate.dtype != out.dtype:
+        raise ValueError("gate and out must be [tokens, width] of one dtype")
+    if weight.shape != (width,) or weight.dtype != torch.float32:
+        raise ValueError(f"weight must be float32 [{width}]")
+    if parts <= 0 or width % parts:
+        raise ValueError(f"a row of {width} cannot be cut into {parts} equal parts")
+    kinds = {"silu": 0, "sigmoid": 1}
+    if gate_kind not in kinds:
+        raise ValueError(f"gate_kind must be one of {sorted(kinds)}")
+    fn = _fn(
+        "einf_gated_norm",
+        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int,
+         c_void_p],
+    )
+    _check(
+        fn(_dev(y, "y"), gate.data_ptr(), _code(gate), _rows_of(gate, "gate"), _dev(weight, "weight"), _dev(out, "out"),
+           tokens, width, parts, float(eps), 1 if gate_first else 0, kinds[gate_kind], _stream()),
+        "gated_norm",
     )
 
 

@@ -19,6 +19,11 @@ LAUNCHERS = {
     "einf_advance_decode": "pointwise",
     "einf_add_bias": "pointwise",
     "einf_zero_fresh_state": "pointwise",
+    "einf_activation": "pointwise",
+    "einf_qkv_norm_store": "pointwise",
+    "einf_conv_silu": "recurrence",
+    "einf_linear_recurrence": "recurrence",
+    "einf_gated_norm": "recurrence",
     "einf_paged_attention_generic": "attention_generic",
     "einf_gemm_simt": "gemm_simt",
     "einf_gemm_tcgen05": "gemm_tcgen05",

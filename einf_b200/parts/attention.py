@@ -25,22 +25,35 @@ class PagedAttention(Mixer):
         hidden, heads, kv_heads, size = (
             spec["hidden_size"], spec["num_heads"], spec["num_kv_heads"], spec["head_size"],
         )
-        specs = {
-            "q_proj.weight": TensorSpec((heads * size, hidden)),
-            "k_proj.weight": TensorSpec((kv_heads * size, hidden)),
-            "v_proj.weight": TensorSpec((kv_heads * size, hidden)),
-            "o_proj.weight": TensorSpec((hidden, heads * size)),
-        }
+        value_size = spec.get("value_head_size") or size
+        own_kv = not spec.get("shared_kv", False)
+        specs = {"q_proj.weight": TensorSpec((heads * size, hidden))}
+        if own_kv:
+            specs["k_proj.weight"] = TensorSpec((kv_heads * size, hidden))
+            specs["v_proj.weight"] = TensorSpec((kv_heads * value_size, hidden))
+        specs["o_proj.weight"] = TensorSpec((hidden, heads * value_size))
         if spec.get("qkv_bias", False):
             specs["q_proj.bias"] = TensorSpec((heads * size,), "bias")
-            specs["k_proj.bias"] = TensorSpec((kv_heads * size,), "bias")
-            specs["v_proj.bias"] = TensorSpec((kv_heads * size,), "bias")
+            if own_kv:
+                specs["k_proj.bias"] = TensorSpec((kv_heads * size,), "bias")
+                specs["v_proj.bias"] = TensorSpec((kv_heads * value_size,), "bias")
         if spec.get("out_bias", False):
             specs["o_proj.bias"] = TensorSpec((hidden,), "bias")
         return specs
 
+    @staticmethod
+    def _is_general(spec) -> bool:
+        """Whether the layer asks for something only the general kernels compute."""
+        return bool(
+            spec.get("qk_unit_eps") is not None or spec.get("softcap") or spec.get("chunk")
+            or spec.get("shared_kv", False)
+            or (spec.get("value_head_size") or spec["head_size"]) != spec["head_size"]
+        )
+
     @classmethod
     def kernel_libraries(cls, spec, runtime):
+        if cls._is_general(spec):
+            return ("pointwise", "attention_generic", "gemm_simt") + cls._product_libraries(runtime)
         if ops.has_fast_attention(runtime.dtype, int(spec["head_size"])):
             # the page size is the engine's choice: ask for both prefill kernels of this head size
             libraries = ops.attention_libraries(int(spec["head_size"]), 16)
@@ -61,38 +74,65 @@ class PagedAttention(Mixer):
         self.window = spec.get("window")
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
-        if self.head_size % 16 or self.head_size > ops.MAX_HEAD_SIZE:
+        self.value_size = int(spec.get("value_head_size") or self.head_size)
+        self.qk_unit_eps = None if spec.get("qk_unit_eps") is None else float(spec["qk_unit_eps"])
+        self.softcap = float(spec["softcap"]) if spec.get("softcap") else None
+        self.chunk = int(spec["chunk"]) if spec.get("chunk") else None
+        self.shared_kv = bool(spec.get("shared_kv", False))
+        self.general = self._is_general(spec)
+        if self.general:
+            if max(self.head_size, self.value_size) > ops.MAX_HEAD_SIZE:
+                raise ops.UnsupportedSize(
+                    f"head sizes {self.head_size}, {self.value_size}: the attention kernels take up to {ops.MAX_HEAD_SIZE}"
+                )
+            if spec["position"].kind != "none":
+                raise ValueError(
+                    "an attention layer with unit-norm heads, a soft cap, a chunked mask, shared keys or values of "
+                    f"another size runs without a position encoding here, not with {spec['position'].kind!r}"
+                )
+        elif self.head_size % 16 or self.head_size > ops.MAX_HEAD_SIZE:
             raise ops.UnsupportedSize(
                 f"head size {self.head_size}: the attention kernels take multiples of 16 up to {ops.MAX_HEAD_SIZE}"
             )
         if self.window is not None and self.window <= 0:
             raise ValueError(f"window must be positive, got {self.window}")
-        matrices = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        if self.chunk is not None and self.chunk <= 0:
+            raise ValueError(f"chunk must be positive, got {self.chunk}")
+        names = ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
+        matrices = [tensors[n + ".weight"] for n in names]
         if len({m.dtype for m in matrices}) > 1:
             matrices = [m.to(torch.float32) for m in matrices]
         self.qkv_weight = runtime.matrix(torch.cat(matrices, dim=0))
         self.qkv_bias = None
         if spec.get("qkv_bias", False):
-            self.qkv_bias = runtime.vector(
-                torch.cat([tensors["q_proj.bias"].float(), tensors["k_proj.bias"].float(), tensors["v_proj.bias"].float()])
-            )
+            self.qkv_bias = runtime.vector(torch.cat([tensors[n + ".bias"].float() for n in names]))
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_nested("position", spec["position"], tensors, runtime)
-        self.fast = ops.has_fast_attention(runtime.dtype, self.head_size)
+        self.fast = not self.general and ops.has_fast_attention(runtime.dtype, self.head_size)
 
     def cache_need(self):
-        return PagedKVNeed(self.num_kv_heads, self.head_size, self.window)
+        value = self.value_size if self.value_size != self.head_size else None
+        return PagedKVNeed(self.num_kv_heads, self.head_size, self.window, value)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         tokens = x.shape[0]
         dtype, device = self.runtime.dtype, x.device
         qkv = ops.project(x, self.qkv_weight, ctx.status)   # [T, width], or split-K partial sums
         q = torch.empty((tokens, self.num_heads, self.head_size), dtype=dtype, device=device)
-        self.position.encode_and_store(
-            qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size
-        )
-        mixed = torch.empty_like(q)
+        if self.general:
+            writes = cache.writes and cache.k is not None and not self.shared_kv
+            ops.qkv_norm_store(
+                qkv, self.qkv_bias, ctx.slots[cache.group] if writes else None, q,
+                cache.k if writes else None, cache.v if writes else None, self.num_heads,
+                0 if self.shared_kv else self.num_kv_heads, self.head_size, self.value_size, self.qk_unit_eps,
+                ctx.status,
+            )
+        else:
+            self.position.encode_and_store(
+                qkv, self.qkv_bias, ctx, cache, q, self.num_heads, self.num_kv_heads, self.head_size
+            )
+        mixed = torch.empty((tokens, self.num_heads, self.value_size), dtype=dtype, device=device)
         self.attend(q, ctx, cache, mixed)
         if self.out_bias is None:
             return ops.project(mixed.view(tokens, -1), self.out_weight, ctx.status)
@@ -110,7 +150,7 @@ class PagedAttention(Mixer):
         return ops.decode_plan(singles, self.num_heads, self.num_kv_heads, self.head_size, page_size, context)
 
     def launch_group(self):
-        return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast)
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast, self.general)
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
         """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode for the
@@ -133,5 +173,5 @@ class PagedAttention(Mixer):
             return
         ops.paged_attention_generic(
             q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.seq_of_token, ctx.positions,
-            out, self.scale, self.window, ctx.status,
+            out, self.scale, self.window, ctx.status, chunk=self.chunk, softcap=self.softcap,
         )

@@ -91,6 +91,12 @@ class PagedKVNeed:
     num_kv_heads: int
     head_size: int
     window: Optional[int] = None
+    #: size of a value head where it differs from the key head's (None: the same)
+    value_head_size: Optional[int] = None
+
+    @property
+    def value_size(self) -> int:
+        return self.head_size if self.value_head_size is None else self.value_head_size
 
 
 @dataclass(frozen=True)
@@ -239,12 +245,19 @@ class PartTensors(dict):
         self.everything = everything
 
 
+def checkpoint_name(spec: PartSpec, local: str) -> str:
+    """The checkpoint name of a part's tensor: the spec's prefix and the local name, or what the
+    spec's ``tensor_names`` puts in the local name's place (an architecture that stores ``q``
+    where the part says ``q_proj.weight``)."""
+    return spec.prefix + spec.get("tensor_names", {}).get(local, local)
+
+
 def build_part(category: str, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> Part:
     """Build the part ``spec`` names from the checkpoint tensors under its prefix."""
     cls = part_class(category, spec.kind)
     local = {}
     for name in cls.tensor_specs(spec):
-        full = spec.prefix + name
+        full = checkpoint_name(spec, name)
         if full not in tensors:
             raise KeyError(f"{category} {spec.kind!r} needs tensor {full!r}")
         local[name] = tensors[full]

@@ -60,5 +60,18 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(x, ctx)
 
 
+@register_part("block", "prenorm_mixer")
+class PreNormMixerBlock(PreNormBlock):
+    """``h += mixer(norm1(h))`` and nothing else: a layer without a feed-forward."""
+
+    @classmethod
+    def part_categories(cls):
+        return {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def forward(self, residual, pending, ctx, cache):
+        x = self._normalise(self.mixer_norm, pending, residual, ctx)
+        return self.mixer.forward(x, ctx, cache)
+
+
 def build_block(layer_spec, tensors, runtime) -> Block:
     return part_class("block", layer_spec.block)(layer_spec, tensors, runtime)

@@ -1,4 +1,5 @@
-"""Gated feed-forward: ``down(act(gate(x)) * up(x))``.
+"""Feed-forwards.  ``gated_mlp``: ``down(act(gate(x)) * up(x))``; ``dense_mlp``: ``down(act(up(x)))``
+with the square of ReLU (``relu2``), the tanh form of GELU, SiLU or ReLU.
 
 Gate and up share one matrix product on the concatenated weight, gate rows
 first (``src/einf/executors/torch/qwen.py:163-172,206-208``); the activation is
@@ -46,4 +47,33 @@ class GatedMLP(FeedForward):
         gate_up = ops.project(x, self.gate_up_weight, ctx.status)   # [T, 2I], or split-K partial sums
         hidden = torch.empty((tokens, self.intermediate_size), dtype=dtype, device=device)
         ops.silu_mul(gate_up, hidden)
+        return ops.project(hidden, self.down_weight, ctx.status)
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    """Two matrices and an activation between them, no gate."""
+
+    @classmethod
+    def tensor_specs(cls, spec):
+        hidden, inter = spec["hidden_size"], spec["intermediate_size"]
+        return {"up_proj.weight": TensorSpec((inter, hidden)), "down_proj.weight": TensorSpec((hidden, inter))}
+
+    @classmethod
+    def kernel_libraries(cls, spec, runtime):
+        return ("pointwise", "gemm_simt") + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.activation = str(spec.get("activation", "relu2"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp knows the activations {sorted(ops.ACTIVATIONS)}, not {self.activation!r}")
+        self.intermediate_size = int(spec["intermediate_size"])
+        self.up_weight = runtime.matrix(tensors["up_proj.weight"])
+        self.down_weight = runtime.matrix(tensors["down_proj.weight"])
+
+    def forward(self, x, ctx):
+        up = ops.project(x, self.up_weight, ctx.status)   # [T, I], or split-K partial sums
+        hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=self.runtime.dtype, device=x.device)
+        ops.activation(up, hidden, self.activation)
         return ops.project(hidden, self.down_weight, ctx.status)

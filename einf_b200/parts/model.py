@@ -13,7 +13,7 @@ import torch
 
 from ..config.specs import ModelSpec, PartSpec, TensorSpec
 from .base import (
-    CacheView, PagedKVNeed, Runtime, StateNeed, StepContext, build_part, part_class, walk_part_specs,
+    CacheView, PagedKVNeed, Runtime, StateNeed, StepContext, build_part, checkpoint_name, part_class, walk_part_specs,
 )
 from .block import build_block
 
@@ -34,11 +34,11 @@ def expected_tensors(model_spec: ModelSpec) -> tuple[dict[str, TensorSpec], dict
     expected: dict[str, TensorSpec] = {}
     for category, spec in _part_specs(model_spec):
         for name, tensor_spec in part_class(category, spec.kind).tensor_specs(spec).items():
-            expected[spec.prefix + name] = tensor_spec
+            expected[checkpoint_name(spec, name)] = tensor_spec
     optional: dict[str, TensorSpec] = {}
     head = model_spec.head
     if head.get("tied_to"):
-        optional[head.prefix + "weight"] = TensorSpec((head["vocab_size"], head["hidden_size"]))
+        optional[checkpoint_name(head, "weight")] = TensorSpec((head["vocab_size"], head["hidden_size"]))
     return expected, optional
 
 
@@ -80,7 +80,7 @@ class DecoderModel:
         head_class = part_class("head", head_spec.kind)
         tied = None
         if head_spec.get("tied_to"):
-            if head_spec["tied_to"] != model_spec.embedding.prefix + "weight":
+            if head_spec["tied_to"] != checkpoint_name(model_spec.embedding, "weight"):
                 raise ValueError(f"head is tied to {head_spec['tied_to']!r}, which is not the embedding table")
             tied = self.embedding.table
             self.head = head_class(head_spec, {}, runtime, tied=tied)
@@ -99,7 +99,8 @@ class DecoderModel:
                 owner_need = entries[owner].need
                 if type(owner_need) is not type(need) or (
                     isinstance(need, PagedKVNeed)
-                    and (need.num_kv_heads, need.head_size) != (owner_need.num_kv_heads, owner_need.head_size)
+                    and (need.num_kv_heads, need.head_size, need.value_size)
+                    != (owner_need.num_kv_heads, owner_need.head_size, owner_need.value_size)
                 ):
                     raise ValueError(
                         f"schedule entry {index} cannot read the cache of entry {owner}: {need} vs {owner_need}"

@@ -3,7 +3,9 @@
 ``residual += pending; out = weight * residual * rsqrt(mean(residual^2) + eps)``,
 all in 32-bit, rounded once into the activation type: the reference's
 ``fused_add_rmsnorm`` (``src/einf/executors/torch/fused_ops.py:41-68``; weight
-initialised to ones, eps inside the root, ``qwen.py:125-132``).
+initialised to ones, eps inside the root, ``qwen.py:125-132``).  With ``offset``
+o in the spec the stored tensor w lies around zero and the weight is ``o + w``
+(added once, in 32-bit, when the part is built).
 """
 from __future__ import annotations
 
@@ -20,7 +22,7 @@ from .base import Norm, register_part
 class RMSNorm(Norm):
     @classmethod
     def tensor_specs(cls, spec):
-        return {"weight": TensorSpec((spec["size"],), "scale")}
+        return {"weight": TensorSpec((spec["size"],), "offset" if spec.get("offset") else "scale")}
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
@@ -31,6 +33,8 @@ class RMSNorm(Norm):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = runtime.vector(tensors["weight"])
+        if spec.get("offset"):
+            self.weight = (self.weight + float(spec["offset"])).contiguous()
 
     #: ``forward`` takes the step's status word (``status=``), where a kernel with a bounded wait reports
     takes_status = True

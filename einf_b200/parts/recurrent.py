@@ -1,0 +1,172 @@
+"""Mixers with a state of fixed size per request instead of keys and values.
+
+Both run the same recurrence kernel (``ops.linear_recurrence``): per head a
+32-bit state ``S [dim, vdim]`` with ``S <- a_t S + k_t (s_t v_t)^T`` and
+``y_t = S^T q_t + skip v_t``, token after token in each request, read from and
+written back to the request's state slot, so a prompt cut into portions and a
+token decoded alone continue where the step before stopped.
+
+``lightning``: linear attention with a constant decay per head.  ``q, k, v =
+silu(W h)``; the heads of ``y`` are normalised together (RMS, weight), multiplied
+by ``sigmoid(W_g h)`` and projected.  One matrix product for q, k, v and the gate.
+
+``mamba2``: the state-space layer of Mamba-2 in its recurrent form.  One product
+gives ``[z | x | B | C | dt]``; x, B and C pass a short causal convolution per
+channel with bias and SiLU (its last ``taps - 1`` inputs are part of the
+request's state); ``dt = softplus(dt + dt_bias)``, ``a_t = exp(-exp(A_log) dt)``,
+``s_t = dt``, ``k = B``, ``q = C`` (shared by the heads of a group), ``v = x``,
+``skip = D``; ``y * silu(z)`` is normalised in ``norm_groups`` parts (RMS, weight)
+and projected.  Decays, step sizes, state, gates and norms are 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.specs import TensorSpec
+from .base import CacheView, Mixer, StateNeed, StepContext, register_part
+
+
+class _RecurrentMixer(Mixer):
+    @classmethod
+    def kernel_libraries(cls, spec, runtime):
+        return ("pointwise", "recurrence", "gemm_simt") + (
+            ("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()
+        )
+
+    def _state(self, cache: CacheView) -> torch.Tensor:
+        if cache.state is None or not cache.writes:
+            raise ValueError(f"a {self.kind} mixer needs a state of its own")
+        return cache.state
+
+
+@register_part("mixer", "lightning")
+class LightningAttention(_RecurrentMixer):
+    @classmethod
+    def tensor_specs(cls, spec):
+        hidden, heads, dim, vdim = spec["hidden_size"], spec["num_heads"], spec["head_size"], spec["value_head_size"]
+        return {
+            "q_proj.weight": TensorSpec((heads * dim, hidden)),
+            "k_proj.weight": TensorSpec((heads * dim, hidden)),
+            "v_proj.weight": TensorSpec((heads * vdim, hidden)),
+            "g_proj.weight": TensorSpec((heads * vdim, hidden)),
+            "o_proj.weight": TensorSpec((hidden, heads * vdim)),
+            "norm.weight": TensorSpec((heads * vdim,), "scale"),
+        }
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.heads = int(spec["num_heads"])
+        self.dim = int(spec["head_size"])
+        self.vdim = int(spec["value_head_size"])
+        self.eps = float(spec["eps"])
+        decay = [float(d) for d in spec["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"{len(decay)} decays for {self.heads} heads")
+        if self.dim > ops.MAX_STATE_ROWS:
+            raise ops.UnsupportedSize(f"head size {self.dim}: the recurrence kernel takes up to {ops.MAX_STATE_ROWS}")
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=runtime.device)
+        matrices = [tensors[n + "_proj.weight"] for n in ("q", "k", "v", "g")]
+        if len({m.dtype for m in matrices}) > 1:
+            matrices = [m.to(torch.float32) for m in matrices]
+        self.in_weight = runtime.matrix(torch.cat(matrices, dim=0))
+        self.out_weight = runtime.matrix(tensors["o_proj.weight"])
+        self.norm_weight = runtime.vector(tensors["norm.weight"])
+
+    def cache_need(self):
+        return StateNeed((self.heads * self.dim * self.vdim,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        tokens = x.shape[0]
+        keys, values = self.heads * self.dim, self.heads * self.vdim
+        proj = ops.project(x, self.in_weight, ctx.status, allow_partial=False)
+        q, k = proj[:, :keys], proj[:, keys:2 * keys]
+        v, gate = proj[:, 2 * keys:2 * keys + values], proj[:, 2 * keys + values:]
+        state = self._state(cache)
+        y = torch.empty((tokens, values), dtype=torch.float32, device=x.device)
+        ops.linear_recurrence(
+            q, k, v, state.view(state.shape[0], self.heads, self.dim, self.vdim), ctx.q_start, ctx.state_slots, y,
+            self.heads, self.heads, self.dim, self.vdim, head_decay=self.decay, silu_inputs=True,
+        )
+        out = torch.empty((tokens, values), dtype=self.runtime.dtype, device=x.device)
+        ops.gated_norm(y, gate, self.norm_weight, out, 1, self.eps, gate_first=False, gate_kind="sigmoid")
+        return ops.project(out, self.out_weight, ctx.status)
+
+
+@register_part("mixer", "mamba2")
+class Mamba2(_RecurrentMixer):
+    @classmethod
+    def _sizes(cls, spec):
+        heads, vdim, state, groups = spec["num_heads"], spec["value_head_size"], spec["state_size"], spec["num_groups"]
+        inner = heads * vdim
+        return heads, vdim, state, groups, inner, inner + 2 * groups * state
+
+    @classmethod
+    def tensor_specs(cls, spec):
+        heads, vdim, state, groups, inner, channels = cls._sizes(spec)
+        hidden, taps = spec["hidden_size"], spec["conv_taps"]
+        return {
+            "in_proj.weight": TensorSpec((inner + channels + heads, hidden)),
+            "conv.weight": TensorSpec((channels, taps), "conv"),
+            "conv.bias": TensorSpec((channels,), "bias"),
+            "dt_bias": TensorSpec((heads,), "dt_bias"),
+            "A_log": TensorSpec((heads,), "a_log"),
+            "D": TensorSpec((heads,), "scale"),
+            "norm.weight": TensorSpec((inner,), "scale"),
+            "o_proj.weight": TensorSpec((hidden, inner)),
+        }
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.heads, self.vdim, self.state_size, self.groups, self.inner, self.channels = self._sizes(spec)
+        self.taps = int(spec["conv_taps"])
+        self.norm_groups = int(spec.get("norm_groups", 1))
+        self.eps = float(spec["eps"])
+        if self.heads % self.groups:
+            raise ValueError(f"{self.heads} heads are not a multiple of {self.groups} groups")
+        if self.inner % self.norm_groups:
+            raise ValueError(f"an inner width of {self.inner} cannot be normalised in {self.norm_groups} equal parts")
+        if not 1 <= self.taps <= ops.MAX_CONV_TAPS:
+            raise ops.UnsupportedSize(f"{self.taps} taps: the convolution kernel takes 1 to {ops.MAX_CONV_TAPS}")
+        if self.state_size > ops.MAX_STATE_ROWS:
+            raise ops.UnsupportedSize(f"state size {self.state_size}: the kernel takes up to {ops.MAX_STATE_ROWS}")
+        self.in_weight = runtime.matrix(tensors["in_proj.weight"])
+        self.out_weight = runtime.matrix(tensors["o_proj.weight"])
+        self.conv_weight = runtime.vector(tensors["conv.weight"])
+        self.conv_bias = runtime.vector(tensors["conv.bias"])
+        self.dt_bias = runtime.vector(tensors["dt_bias"])
+        self.a_log = runtime.vector(tensors["A_log"])
+        self.skip = runtime.vector(tensors["D"])
+        self.norm_weight = runtime.vector(tensors["norm.weight"])
+        self.state_floats = self.heads * self.state_size * self.vdim
+
+    def cache_need(self):
+        # the recurrent state, then the convolution's last taps-1 inputs [taps-1, channels]
+        return StateNeed((self.state_floats + (self.taps - 1) * self.channels,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        tokens, device = x.shape[0], x.device
+        inner, channels, heads = self.inner, self.channels, self.heads
+        proj = ops.project(x, self.in_weight, ctx.status, allow_partial=False)
+        z, xbc, dt_raw = proj[:, :inner], proj[:, inner:inner + channels], proj[:, inner + channels:]
+        state = self._state(cache)
+        slots = state.shape[0]
+        recurrent = state[:, :self.state_floats].view(slots, heads, self.state_size, self.vdim)
+        conv_state = state[:, self.state_floats:].view(slots, self.taps - 1, channels)
+        conv = torch.empty((tokens, channels), dtype=proj.dtype, device=device)
+        dt = torch.empty((tokens, heads), dtype=torch.float32, device=device)
+        decay = torch.empty_like(dt)
+        ops.conv_silu(
+            xbc, self.conv_weight, self.conv_bias, conv_state, ctx.seq_of_token, ctx.q_start, ctx.state_slots, conv,
+            dt_raw, self.dt_bias, self.a_log, dt, decay,
+        )
+        width = self.groups * self.state_size
+        xs, b, c = conv[:, :inner], conv[:, inner:inner + width], conv[:, inner + width:]
+        y = torch.empty((tokens, inner), dtype=torch.float32, device=device)
+        ops.linear_recurrence(
+            c, b, xs, recurrent, ctx.q_start, ctx.state_slots, y, heads, self.groups, self.state_size, self.vdim,
+            token_decay=decay, token_scale=dt, skip=self.skip,
+        )
+        out = torch.empty((tokens, inner), dtype=self.runtime.dtype, device=device)
+        ops.gated_norm(y, z, self.norm_weight, out, self.norm_groups, self.eps, gate_first=True, gate_kind="silu")
+        return ops.project(out, self.out_weight, ctx.status)

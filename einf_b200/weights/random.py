@@ -3,7 +3,9 @@
 The reference has no such mode (its tests rely on ``nn.Linear`` default
 initialisation under ``torch.manual_seed``, ``tests/test_torch_qwen.py:72-75``).
 Matrices and biases are drawn N(0, ``init_std``), norm weights
-1 + N(0, ``init_scale_std``), one tensor after another in sorted name order
+1 + N(0, ``init_scale_std``) (around zero for a norm that adds the one itself;
+convolution taps, step-size biases and rate logarithms of a state-space layer
+in the ranges such layers are initialised to), one tensor after another in sorted name order
 from one seeded CPU generator, and stored in bfloat16, so every reader of the
 folder sees the same values.
 """
@@ -44,6 +46,15 @@ def random_tensors(
         values = torch.randn(spec.shape, generator=generator, dtype=torch.float32, device=device)
         if spec.role == "scale":
             values = 1.0 + scale_std * values
+        elif spec.role == "offset":        # a norm weight stored around zero
+            values = scale_std * values
+        elif spec.role == "conv":          # taps of a short convolution
+            values = values / (2.0 * spec.shape[-1] ** 0.5)
+        elif spec.role == "dt_bias":       # softplus of it lies between 0.001 and 0.1
+            step = torch.exp(torch.sigmoid(values) * 4.6 - 6.9)
+            values = step + torch.log(-torch.expm1(-step))
+        elif spec.role == "a_log":         # the logarithm of a rate between 1 and 16
+            values = torch.log(1.0 + 15.0 * torch.sigmoid(values))
         else:
             values = std * values
         tensors[name] = values.to(dtype)
