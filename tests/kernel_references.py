@@ -94,7 +94,8 @@ def project(x, weight, status, out_dtype=None, allow_partial=True):
     return out
 
 
-def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status):
+def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status,
+                            chunk=None, softcap=None):
     tokens, num_heads, head_size = q.shape
     _, num_kv_heads, page_size, _ = k_cache.shape
     groups = num_heads // num_kv_heads
@@ -102,6 +103,8 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         r = int(seq_of_token[t])
         pos = int(positions[t])
         lo = max(0, pos - window + 1) if window else 0
+        if chunk:
+            lo = max(lo, pos // chunk * chunk)
         keys = torch.arange(lo, pos + 1, device=q.device)
         pages = block_table[r, (keys // page_size).long()].long()
         offsets = (keys % page_size).long()
@@ -110,8 +113,118 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         k = k.repeat_interleave(groups, dim=1)
         v = v.repeat_interleave(groups, dim=1)
         scores = torch.einsum("hd,nhd->hn", q[t].float(), k) * scale
+        if softcap:
+            scores = softcap * torch.tanh(scores / softcap)
         probabilities = torch.softmax(scores, dim=-1)
         out[t] = torch.einsum("hn,nhd->hd", probabilities, v).to(out.dtype)
+
+
+def _summed(x):
+    x = x.float()
+    return x.sum(0) if x.dim() == 3 else x
+
+
+def activation(x, out, kind):
+    z = _summed(x)
+    if kind == "relu2":
+        y = torch.clamp(z, min=0) ** 2
+    elif kind == "gelu_tanh":
+        y = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    elif kind == "silu":
+        y = z / (1 + torch.exp(-z))
+    elif kind == "relu":
+        y = torch.clamp(z, min=0)
+    else:
+        raise ValueError(kind)
+    out.copy_(y.to(out.dtype))
+
+
+def qkv_norm_store(qkv, bias, slots, q_out, k_cache, v_cache, num_heads, num_kv_heads, key_size, value_size,
+                   unit_eps, status):
+    values = _summed(qkv)
+    tokens = values.shape[0]
+    if bias is not None:
+        values = values + bias
+    q, k, v = values.split([num_heads * key_size, num_kv_heads * key_size, num_kv_heads * value_size], dim=-1)
+    q = q.reshape(tokens, num_heads, key_size)
+    k = k.reshape(tokens, num_kv_heads, key_size)
+    v = v.reshape(tokens, num_kv_heads, value_size)
+    if unit_eps is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + unit_eps)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + unit_eps)
+    q_out.copy_(q.reshape(q_out.shape).to(q_out.dtype))
+    if slots is not None and num_kv_heads:
+        page_size = k_cache.shape[2]
+        keep = slots >= 0
+        page = (slots[keep] // page_size).long()
+        offset = (slots[keep] % page_size).long()
+        k_cache[page, :, offset, :] = k[keep].to(k_cache.dtype)
+        v_cache[page, :, offset, :] = v[keep].to(v_cache.dtype)
+
+
+def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, out, dt_raw=None, dt_bias=None,
+              a_log=None, dt_out=None, decay_out=None):
+    taps = weight.shape[1]
+    xf = x.float()
+    for r in range(state_slots.shape[0]):
+        first, last = int(q_start[r]), int(q_start[r + 1])
+        slot = int(state_slots[r])
+        if last <= first:
+            continue
+        history = conv_state[slot].clone() if slot >= 0 else torch.zeros(taps - 1, x.shape[1])
+        line = torch.cat([history, xf[first:last]], dim=0)            # [taps - 1 + n, channels]
+        for i in range(last - first):
+            acc = (line[i:i + taps].T * weight).sum(dim=1)
+            if bias is not None:
+                acc = acc + bias
+            out[first + i] = (acc / (1 + torch.exp(-acc))).to(out.dtype)
+        if slot >= 0 and taps > 1:
+            conv_state[slot] = line[-(taps - 1):]
+    if dt_raw is not None:
+        dt = torch.nn.functional.softplus(dt_raw.float() + dt_bias)
+        dt_out.copy_(dt)
+        decay_out.copy_(torch.exp(-torch.exp(a_log) * dt))
+
+
+def linear_recurrence(q, k, v, state, q_start, state_slots, y, heads, groups, dim, vdim, head_decay=None,
+                      token_decay=None, token_scale=None, skip=None, silu_inputs=False):
+    def act(t):
+        t = t.float()
+        return t / (1 + torch.exp(-t)) if silu_inputs else t
+
+    tokens = v.shape[0]
+    qf, kf = act(q).reshape(tokens, groups, dim), act(k).reshape(tokens, groups, dim)
+    vf = act(v).reshape(tokens, heads, vdim)
+    per_group = heads // groups
+    for r in range(state_slots.shape[0]):
+        first, last = int(q_start[r]), int(q_start[r + 1])
+        slot = int(state_slots[r])
+        for h in range(heads):
+            S = state[slot, h].clone() if slot >= 0 else torch.zeros(dim, vdim)
+            g = h // per_group
+            for t in range(first, last):
+                a = head_decay[h] if head_decay is not None else token_decay[t, h]
+                s = token_scale[t, h] if token_scale is not None else 1.0
+                S = a * S + torch.outer(kf[t, g], s * vf[t, h])
+                row = S.T @ qf[t, g]
+                if skip is not None:
+                    row = row + skip[h] * vf[t, h]
+                y[t, h * vdim:(h + 1) * vdim] = row
+            if slot >= 0 and last > first:
+                state[slot, h] = S
+
+
+def gated_norm(y, gate, weight, out, parts, eps, gate_first, gate_kind):
+    g = gate.float()
+    g = g / (1 + torch.exp(-g)) if gate_kind == "silu" else torch.sigmoid(g)
+    u = y * g if gate_first else y
+    tokens, width = y.shape
+    cut = u.reshape(tokens, parts, width // parts)
+    cut = cut * torch.rsqrt(cut.pow(2).mean(-1, keepdim=True) + eps)
+    result = cut.reshape(tokens, width) * weight
+    if not gate_first:
+        result = result * g
+    out.copy_(result.to(out.dtype))
 
 
 def argmax(logits, tokens):
@@ -201,7 +314,8 @@ def ensure_built(names):
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
-    "zero_fresh_state", "has_fast_attention",
+    "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
+    "gated_norm",
 )
 
 
