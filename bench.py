@@ -131,7 +131,8 @@ def decode_requests(batch: int, context: int, runner, manager, tag: str):
             raise RuntimeError("the pool is too small for the benchmark")
         requests.append(SimpleNamespace(
             request_id=name, input_token_ids=[int(torch.randint(3, 150000, (1,), generator=generator))],
-            start_position=context, block_tables=[manager.block_table(name, 0)], state_slot=-1, need_sample=True))
+            start_position=context, block_tables=[manager.block_table(name, 0)], state_slot=manager.state_slot(name),
+            need_sample=True))
     return requests
 
 
@@ -199,7 +200,8 @@ def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 7) -> dic
         name = f"prefill{attempt}"
         manager.reserve(name, 0, tokens)
         request = SimpleNamespace(request_id=name, input_token_ids=ids, start_position=0,
-                                  block_tables=[manager.block_table(name, 0)], state_slot=-1, need_sample=True)
+                                  block_tables=[manager.block_table(name, 0)], state_slot=manager.state_slot(name),
+                                  need_sample=True)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -490,6 +492,166 @@ def run_mixed_15b(args) -> dict:
             "tokens_per_s": round(544 / ms * 1e3, 1), "decode_tokens_per_s": round(32 / ms * 1e3, 1),
             "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4),
             "flops_frac": round(chunk_flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "steps": args.steps}
+
+
+def tepavik_sizes(width: int, ff: int, heads: int, kv_heads: int, size: int, layers: int, vocab: int, chunk: int) -> dict:
+    """A Tepavik configuration at the layer sizes of a Qwen2 model: attention, lightning and
+    Mamba-2 layers in turn, every mixer about as wide as the attention layer it stands for."""
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": size, "vdim": size,
+                                                "scale": size ** -0.5 * 8, "softcap": 50.0, "mask": {"size": chunk}}}
+    lightning = {"type": "lightning", "mixer": {"heads": heads, "dim": size, "vdim": size,
+                                                "decay": [1.0 - 2.0 ** -(3 + 6 * h / heads) for h in range(heads)]}}
+    mamba = {"type": "mamba2", "mixer": {"heads": heads * size // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+                                         "norm_groups": 1}}
+    out = []
+    for index in range(layers):
+        layer = dict((attention, lightning, mamba)[index % 3])
+        layer["mlp"] = {"kind": "dense", "ff": ff}
+        out.append(layer)
+    return {"architecture": "Tepavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
+def run_tepavik(args) -> dict:
+    """Prefill and decode throughput of the Tepavik design at the layer sizes of the 0.5B and 1.5B
+    models (random weights, twelve layers unless --layers says otherwise: four each of chunked
+    attention, lightning and Mamba-2), beside Qwen2 at the same width, heads, feed-forward width,
+    layers and vocabulary; then the design's own kernels alone, each beside the kernel of the
+    Qwen2 path that does the like job at the same sizes, in microseconds and as a fraction of
+    the copy bandwidth or of a library product's rate."""
+    import torch
+
+    from einf_b200 import ops
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    layers = args.layers or 12
+    result = {"scenario": "tepavik", "layers": layers, "context": CONTEXT, "chunk": 1024}
+    shapes = {"0.5b": (896, 4864, 14, 2, 64), "1.5b": (1536, 8960, 12, 2, 128)}
+    for name, (width, ff, heads, kv_heads, size) in shapes.items():
+        qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=False)
+        vocab = qwen["vocab_size"]
+        for arch, cfg in (("tepavik", tepavik_sizes(width, ff, heads, kv_heads, size, layers, vocab, 1024)), ("qwen2", qwen)):
+            pages = 64 * (CONTEXT // PAGE + 2) + 64
+            runner = ModelRunner.from_random(
+                config_from_dict(cfg), 0,
+                EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=8192,
+                             max_prefill_chunk_len=8192, max_requests=64))
+            manager = CacheManager(runner.group_specs(), runner.num_state_slots)
+            sampler = Sampler(runner.runtime.device, 64)
+            for tokens in (2048, 8192):
+                timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
+                result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
+                result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
+            for batch in (1, 8, 64):
+                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup)
+                result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
+                result[f"{name}_{arch}_decode_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
+            del runner, manager, sampler
+            torch.cuda.empty_cache()
+    result["kernels"] = tepavik_kernels(peak)
+    return result
+
+
+def tepavik_kernels(peak: dict) -> dict:
+    """The design's kernels alone (microseconds per launch in a CUDA graph of launches on rotating
+    buffers larger than the L2) with the bytes or flops each must move, beside the like kernel of
+    the Qwen2 path."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out: dict = {}
+    gbs, tflops = peak["hbm_gbs"], peak["bf16_tflops"]
+
+    def rate(key, us, nbytes=0, flops=0):
+        out[key + "_us"] = round(us, 1)
+        if nbytes:
+            out[key + "_hbm_frac"] = round(nbytes / us / 1e3 / gbs, 3)
+        if flops:
+            out[key + "_flops_frac"] = round(flops / us / 1e6 / tflops, 4)
+
+    for heads, kv_heads, size in ((14, 2, 64), (12, 2, 128)):
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)) + ["recurrence", "pointwise"])
+        tag = f"h{heads}_d{size}"
+        # --- attention, prompt of 2,048 tokens: chunked and capped beside the plain causal kernel
+        tokens, chunk = 2048, 1024
+        pages = tokens // PAGE
+        launches = 8
+        k = torch.randn(pages * launches + 4, kv_heads, PAGE, size, device=device).bfloat16()
+        v = torch.randn_like(k)
+        q = torch.randn(tokens, heads, size, device=device).bfloat16()
+        o = torch.empty_like(q)
+        tables = [torch.arange(i * pages, (i + 1) * pages, dtype=torch.int32, device=device).view(1, -1) for i in range(launches)]
+        tiles = torch.tensor([[0, first, 128, first] for first in range(0, tokens, 128)], dtype=torch.int32, device=device)
+        turn = [0]
+
+        def prefill(chunk=None, softcap=None):
+            table = tables[turn[0] % launches]
+            turn[0] += 1
+            ops.paged_prefill_attention(q, k, v, table, tiles, o, size ** -0.5, None, status, cached_before=0,
+                                        chunk=chunk, softcap=softcap)
+
+        causal_flops = 4 * heads * size * tokens * tokens / 2
+        chunked_flops = 4 * heads * size * (tokens // chunk) * chunk * chunk / 2
+        rate(tag + "_prefill_attention_causal", _graph_time_us(prefill, launches), flops=causal_flops)
+        rate(tag + "_prefill_attention_chunked_capped", _graph_time_us(lambda: prefill(chunk, 50.0), launches), flops=chunked_flops)
+        rate(tag + "_prefill_attention_capped", _graph_time_us(lambda: prefill(None, 50.0), launches), flops=causal_flops)
+        # --- attention, decode of 8 and 64 requests at 4,096 tokens
+        for batch in (8, 64):
+            context = CONTEXT
+            pages = context // PAGE
+            layer_bytes = 2 * batch * context * kv_heads * size * 2
+            launches = max(4, min(12, int(1.5e9 // layer_bytes)))
+            k = torch.randn(pages * batch * launches + 2, kv_heads, PAGE, size, device=device).bfloat16()
+            v = torch.randn_like(k)
+            qd = torch.randn(batch, heads, size, device=device).bfloat16()
+            od = torch.empty_like(qd)
+            dtables = [torch.arange(i * pages * batch, (i + 1) * pages * batch, dtype=torch.int32, device=device).view(batch, pages)
+                       for i in range(launches)]
+            seq = torch.arange(batch, dtype=torch.int32, device=device)
+            positions = torch.full((batch,), context - 1, dtype=torch.int32, device=device)
+
+            def decode(chunk=None, softcap=None):
+                table = dtables[turn[0] % launches]
+                turn[0] += 1
+                ops.paged_decode_attention_auto(qd, k, v, table, seq, positions, od, size ** -0.5, None, status,
+                                                max_context=context, chunk=chunk, softcap=softcap)
+
+            rate(f"{tag}_decode_attention_b{batch}_causal", _graph_time_us(decode, launches), nbytes=layer_bytes)
+            rate(f"{tag}_decode_attention_b{batch}_chunked_capped", _graph_time_us(lambda: decode(1024, 50.0), launches),
+                 nbytes=layer_bytes // 4)
+            del k, v
+        # --- the recurrence: a prompt of 2,048 tokens, and single tokens of 8 and 64 requests
+        for label, r_heads, groups, dim, vdim in (("lightning", heads, heads, size, size),
+                                                  ("mamba2", heads * size // 64, 1, 128, 64)):
+            state_floats = r_heads * dim * vdim
+            for what, lengths in (("prompt2048", [2048]), ("decode_b8", [1] * 8), ("decode_b64", [1] * 64)):
+                requests, tokens = len(lengths), sum(lengths)
+                copies = max(2, min(16, int(3e8 // (requests * state_floats * 4))))
+                states = [torch.zeros(requests, r_heads, dim, vdim, device=device) for _ in range(copies)]
+                qq = (torch.randn(tokens, groups * dim, device=device) * 0.1).bfloat16()
+                kk = (torch.randn(tokens, groups * dim, device=device) * 0.1).bfloat16()
+                vv = torch.randn(tokens, r_heads * vdim, device=device).bfloat16()
+                y = torch.empty(tokens, r_heads * vdim, device=device)
+                starts = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+                slots = torch.arange(requests, dtype=torch.int32, device=device)
+                decay = torch.full((r_heads,), 0.99, device=device)
+
+                def scan():
+                    state = states[turn[0] % copies]
+                    turn[0] += 1
+                    ops.linear_recurrence(qq, kk, vv, state, starts, slots, y, r_heads, groups, dim, vdim, head_decay=decay)
+
+                us = _graph_time_us(scan, copies)
+                moved = 2 * requests * state_floats * 4 + tokens * (2 * groups * dim + r_heads * vdim) * 2 + tokens * r_heads * vdim * 4
+                rate(f"{tag}_{label}_recurrence_{what}", us, nbytes=moved, flops=4 * tokens * state_floats)
+    out["status"] = int(status)
+    return out
 
 
 def run_decode_sizes(args) -> dict:
@@ -828,7 +990,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -864,7 +1026,7 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes,
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik,
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)

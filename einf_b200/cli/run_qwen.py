@@ -1,4 +1,6 @@
-"""Command line: run a Qwen2.5 model folder (or random weights) to generated tokens.
+"""Command line: run a model folder (or random weights) to generated tokens.  The architecture is
+the one the folder's ``config.json`` names (Qwen2 / Qwen2.5, Tepavik); ``bin/run_qwen`` and
+``bin/run_model`` are the same program.
 
 Options keep the reference's names and meanings where it has them
 (``scripts/run_qwen.py:33-74``): ``--model-dir``, ``--prompt``, ``--max-new-len``,
@@ -30,8 +32,9 @@ from pathlib import Path
 DEFAULT_MODEL_DIR = Path(os.environ.get("EINF_MODEL_DIR", str(Path.home() / "models" / "Qwen2.5-0.5B")))
 
 
-def parse_args(argv=None) -> argparse.Namespace:
-    parser = argparse.ArgumentParser(prog="run_qwen", description="Run Qwen2.5 through einf_b200")
+def parse_args(argv=None, prog: str = "run_qwen") -> argparse.Namespace:
+    parser = argparse.ArgumentParser(
+        prog=prog, description="Run a model folder through einf_b200 (the architecture is read from its config.json)")
     parser.add_argument("--model-dir", type=Path, default=DEFAULT_MODEL_DIR)
     parser.add_argument("--prompt", default="The capital of France is")
     parser.add_argument("--prompt-ids", default=None, help="comma-separated token ids; no tokenizer is needed then")
@@ -41,6 +44,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--num-blocks", type=int, default=256)
     parser.add_argument("--max-batch-len", type=int, default=128)
     parser.add_argument("--max-prefill-chunk-len", type=int, default=128)
+    parser.add_argument("--max-requests", type=int, default=64,
+                        help="most requests that hold cache at a time (block-table rows, state slots)")
     parser.add_argument("--policy", choices=("fcfs", "decode_first"), default="fcfs")
     parser.add_argument("--decode-lookahead", type=int, default=1,
                         help="decode steps per report to the host (not an option of the reference; 1 is its behaviour)")
@@ -69,8 +74,8 @@ def _tokenizer(model_dir: Path):
         return None
 
 
-def main(argv=None) -> int:
-    args = parse_args(argv)
+def main(argv=None, prog: str = "run_qwen") -> int:
+    args = parse_args(argv, prog)
     if args.compare_reference and args.temperature != 0.0:
         print("--compare-reference compares greedy tokens: leave --temperature at 0", file=sys.stderr)
         return 2
@@ -101,6 +106,7 @@ def main(argv=None) -> int:
             dtype=args.dtype, block_len=args.block_len, num_blocks=args.num_blocks,
             max_batch_len=args.max_batch_len, max_prefill_chunk_len=args.max_prefill_chunk_len,
             policy=args.policy, device=args.device, decode_lookahead=args.decode_lookahead,
+            max_requests=args.max_requests,
         ),
         eos_token_ids=() if args.ignore_eos else None,
     )
@@ -131,7 +137,7 @@ def main(argv=None) -> int:
             EngineConfig(
                 dtype="float32", block_len=args.block_len, num_blocks=-(-total // args.block_len) + 1,
                 max_batch_len=max(total, 8), max_prefill_chunk_len=max(total, 8), policy="fcfs",
-                device=args.device, decode_lookahead=1, use_cuda_graphs=False,
+                device=args.device, decode_lookahead=1, use_cuda_graphs=False, max_requests=args.max_requests,
             ),
             eos_token_ids=() if args.ignore_eos else None,
         )

@@ -278,6 +278,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// A raw score (q . k) as the exponent of 2 the softmax takes: score * scale * log2(e), or with a soft cap z
+// z * tanh(score * scale / z) * log2(e).  tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1): the hardware's exponential
+// and reciprocal, good to about 1e-6 of the cap (its own tanh.approx is good to 5e-4 only).
+struct ScoreScale {
+  float scale_log2;     // scale * log2(e)
+  float tanh_in;        // 2 * log2(e) * scale / cap, or 0 without a cap
+  float cap_log2;       // cap * log2(e)
+};
+__device__ __forceinline__ float capped(float raw, const ScoreScale& c) {
+  const float e = fast_exp2(raw * c.tanh_in);
+  float inv;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e + 1.f));
+  return fmaf(-2.f * c.cap_log2, inv, c.cap_log2);
+}
+__device__ __forceinline__ float score_log2(float raw, const ScoreScale& c) {
+  return c.tanh_in != 0.f ? capped(raw, c) : raw * c.scale_log2;
+}
+__device__ __forceinline__ ScoreScale make_score_scale(float scale, float softcap) {
+  ScoreScale c;
+  c.scale_log2 = scale * 1.4426950408889634f;
+  c.tanh_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
+  c.cap_log2 = softcap * 1.4426950408889634f;
+  return c;
+}
+// The first position a token at `pos` may see: the later of its window's and its chunk's start.
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+  return lo;
+}
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -332,7 +362,8 @@ struct TcAttentionParams {
   __nv_bfloat16* out;       // [tokens, heads, D]
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
-  float scale_log2;
+  int chunk;                // chunked mask: a row sees only the keys of its own block of this many positions (0: off)
+  float scale, softcap;     // scores are multiplied by scale; with a cap z they become z * tanh(score / z)
 };
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -370,7 +401,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
   const int request = tile_info.x, token0 = tile_info.y, rows = tile_info.z, pos0 = tile_info.w;
   const int* table = p.block_table + (size_t)request * p.table_width;
   const int last_pos = pos0 + rows - 1;
-  int k_begin = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  int k_begin = first_visible(pos0, p.window, p.chunk);
   k_begin = k_begin / p.page_size * p.page_size;          // tiles start on a page edge
   int k_end = last_pos + 1;
   // A prompt portion of a few row tiles does not fill the GPU (four tiles of twelve heads are 48
@@ -543,6 +574,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     const int g = warp >= 6 ? 1 : 0;                           // warpgroup: tiles g, g + 2, ...; dims g * D / 2 ... of the output
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int pos = r < rows ? pos0 + r : -1;
+    const int pos_lo = (p.window > 0 || p.chunk > 0) && pos >= 0 ? first_visible(pos, p.window, p.chunk) : 0;
+    const ScoreScale sc = make_score_scale(p.scale, p.softcap);
+    const bool has_cap = p.softcap > 0.f;
     constexpr int kDimsHere = D / 2;
     const uint32_t s_tile = tmem_s(g), o_acc = tmem_o(g) + lane_addr;
     // P and O are scaled by a reference m_ref: the maximum of the row's first tile, and after that
@@ -608,7 +642,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       // A tile that lies wholly before this row's position (and inside its window) needs no mask;
       // in a tile on the diagonal or at a window's edge, column c of the tile is set to -inf
       // (probability 2^-inf = 0) unless c_lo <= c <= c_hi, before anything else looks at it.
-      const int c_hi = pos - key0, c_lo = p.window > 0 ? pos - p.window + 1 - key0 : 0;
+      const int c_hi = pos - key0, c_lo = pos_lo - key0;
       const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && c_lo <= 0);
       auto mask = [&](float* sv, int c0) {
         const int hi = c_hi - c0, lo = c_lo - c0;
@@ -638,10 +672,11 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           }
           wait_o_quiet();
           // the scale is positive: max and scale commute
-          move_reference(fmaxf(m_ref, tile_max * p.scale_log2), done > 0);
+          // the scale is positive and the cap grows with the score: max and either commute
+          move_reference(fmaxf(m_ref, tile_max == -INFINITY ? -INFINITY : score_log2(tile_max, sc)), done > 0);
         }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
+        const float2 scale2 = make_float2(sc.scale_log2, sc.scale_log2), shift2 = make_float2(-m_use, -m_use);
         sum2 = make_float2(0.f, 0.f);
         auto store = [&](const float* sv, int c0) {
           uint32_t packed[16];
@@ -672,6 +707,19 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           // layout (32 keys = four 16-byte chunks of this row inside slice c0 / 64)
           auto exps = [&](float* sv, int c0, bool masked_already) {
             if (kMasked && !masked_already) mask(sv, c0);
+            if (has_cap) {
+              // a masked score is -inf: 2^-inf = 0, the reciprocal of 1 is 1, the capped score -cap; it
+              // has to stay -inf
+#pragma unroll
+              for (int c = 0; c < 32; ++c) sv[c] = sv[c] == -INFINITY ? -INFINITY : capped(sv[c], sc) - m_use;
+#pragma unroll
+              for (int c = 0; c < 32; c += 2) {
+                sv[c] = fast_exp2(sv[c]);
+                sv[c + 1] = fast_exp2(sv[c + 1]);
+                sum2 = __fadd2_rn(sum2, make_float2(sv[c], sv[c + 1]));
+              }
+              return;
+            }
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), scale2, shift2);
@@ -710,7 +758,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
               for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], sb[c]);
               const float last_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
               again = !walked && __any_sync(0xffffffffu, !(sum2.x + sum2.y <= kSumLimit) ||
-                                                             fmaf(last_max, p.scale_log2, -m_use) > kLastLimit);
+                                                             (last_max == -INFINITY ? -INFINITY : score_log2(last_max, sc) - m_use) > kLastLimit);
               if (!again) {
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 bar_arrive(s_free(g));
@@ -905,7 +953,8 @@ struct TcDecodeParams {
   __nv_bfloat16* out;       // [tokens, heads, D]
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
-  float scale_log2;
+  int chunk;                // see TcAttentionParams
+  float scale, softcap;
   // A token's keys split over `splits` clusters, which meet in global memory: every cluster writes its
   // unnormalised share [16 heads][D + 2] (the accumulator, then maximum and sum) to split_out, every
   // CTA counts itself in split_count, and the CTA that finds itself the last adds the shares up.
@@ -978,7 +1027,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   // for it where it first needs one of those.
   const int t = p.token_list ? p.token_list[blockIdx.z] : blockIdx.z;
   const int pos = p.positions[t];
-  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  const int lo = first_visible(pos, p.window, p.chunk);
   const int lo_page = lo / p.page_size * p.page_size;         // tiles start on a page edge
   const int split = kSplit ? (int)(blockIdx.x / csize) : 0;    // which of the token's clusters this is
   const int parts = kSplit ? (int)csize * p.splits : (int)csize;
@@ -1164,6 +1213,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     // Every softmax warp walks every tile, whatever happens: the four meet inside the loop at a
     // hardware barrier.  After a bounded wait that gave up (the status word then fails the step)
     // nothing is waited for any more and the results are garbage, but the walk goes on to its end.
+    const ScoreScale sc = make_score_scale(p.scale, p.softcap);
     for (int i = 0; i < num_tiles; ++i) {
       const int j = k_begin + i * kBlockKV + r;                  // this thread's key
       const bool visible = j >= lo && j < k_end;
@@ -1177,7 +1227,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         float red[kDecHeads];
 #pragma unroll
         for (int h = 0; h < kDecHeads; ++h) {
-          sv[h] = visible ? sv[h] * p.scale_log2 : -INFINITY;
+          sv[h] = visible ? score_log2(sv[h], sc) : -INFINITY;
           red[h] = sv[h];
         }
         const float m = warp_reduce16<true>(red, lane);
@@ -1437,7 +1487,8 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
                                                     const int* block_table, const int* tiles, int num_tiles,
                                                     void* out, int num_tokens, int num_heads, int num_kv_heads,
                                                     int page_size, int num_pages, int table_width, float scale,
-                                                    int window, int cluster, int* status, cudaStream_t stream) {
+                                                    int window, int chunk, float softcap, int cluster, int* status,
+                                                    cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (cluster < 1 || cluster > 8) return (int)cudaErrorInvalidValue;
   if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
@@ -1465,7 +1516,9 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   p.num_pages = num_pages;
   p.table_width = table_width;
   p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.chunk = chunk;
+  p.scale = scale;
+  p.softcap = softcap;
   cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return (int)e;
@@ -1532,8 +1585,9 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
                                                    const int* positions, const int* token_list, void* out,
                                                    int num_tokens, int num_heads, int num_kv_heads, int page_size,
                                                    int num_pages, int table_width, float scale, int window,
-                                                   int cluster, int splits, float* split_out, int* split_count,
-                                                   int* status, cudaStream_t stream) {
+                                                   int chunk, float softcap, int cluster, int splits,
+                                                   float* split_out, int* split_count, int* status,
+                                                   cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (cluster < 1 || cluster > kDecMaxCluster) return (int)cudaErrorInvalidValue;
   if (splits < 1 || splits > kDecMaxSplits || (splits > 1 && (!split_out || !split_count))) return (int)cudaErrorInvalidValue;
@@ -1563,7 +1617,9 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   p.num_pages = num_pages;
   p.table_width = table_width;
   p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.chunk = chunk;
+  p.scale = scale;
+  p.softcap = softcap;
   p.splits = splits;
   p.split_out = split_out;
   p.split_count = split_count;

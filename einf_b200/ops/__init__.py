@@ -1028,17 +1028,23 @@ def paged_decode_attention_auto(
     status: torch.Tensor,
     token_list: Optional[torch.Tensor] = None,
     max_context: Optional[int] = None,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
 ) -> None:
     """Decode attention by the kernel, cluster size and number of clusters per token that
     ``decode_plan`` picks for this batch; ``max_context`` is the longest context among the
-    tokens (a window shortens it), as the host knows it."""
+    tokens (a window or a chunk shortens it), as the host knows it.  ``chunk`` and ``softcap`` (see
+    :func:`paged_attention_generic`) are the tcgen05 kernel's alone."""
     tokens = token_list.shape[0] if token_list is not None else q.shape[0]
-    if window and max_context is not None:
-        max_context = min(max_context, int(window))
+    for bound in (window, chunk):
+        if bound and max_context is not None:
+            max_context = min(max_context, int(bound))
     kernel, cluster, splits = decode_plan(tokens, q.shape[1], k_cache.shape[1], q.shape[2], k_cache.shape[2], max_context)
     if kernel == "tcgen05":
         paged_decode_attention_tcgen05(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
-                                       cluster, status, token_list, splits)
+                                       cluster, status, token_list, splits, chunk=chunk, softcap=softcap)
+    elif chunk or softcap:
+        raise UnsupportedSize("a chunked mask or a soft cap needs the tcgen05 decode kernel (head size 64 or 128)")
     else:
         paged_decode_attention_cluster(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
                                        cluster, status, token_list)
@@ -1122,6 +1128,8 @@ def paged_decode_attention_tcgen05(
     status: torch.Tensor,
     token_list: Optional[torch.Tensor] = None,
     splits: int = 1,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
 ) -> None:
     """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
     (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
@@ -1147,7 +1155,8 @@ def paged_decode_attention_tcgen05(
         shares, counters = _decode_split_workspace(tokens * num_kv_heads * head_blocks, splits, q.device)
     fn = _fn(
         "einf_paged_decode_attention_tcgen05",
-        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p],
         f"HEAD_SIZE={head_size}",
     )
     _check(
@@ -1155,7 +1164,8 @@ def paged_decode_attention_tcgen05(
            _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
            _opt(positions, "positions", torch.int32), _opt(token_list, "token_list", torch.int32), _dev(out, "out"),
            tokens, num_heads, num_kv_heads, page_size,
-           num_pages, block_table.shape[1], float(scale), int(window) if window else 0, cluster,
+           num_pages, block_table.shape[1], float(scale), int(window) if window else 0,
+           int(chunk) if chunk else 0, float(softcap) if softcap else 0.0, cluster,
            splits, shares.data_ptr() if splits > 1 else None, counters.data_ptr() if splits > 1 else None,
            _dev(status, "status"), _stream()),
         "paged_decode_attention_tcgen05",
@@ -1216,6 +1226,8 @@ def paged_prefill_attention(
     use_tcgen05: Optional[bool] = None,
     prefill_cluster: int = 0,
     cached_before: Optional[int] = None,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
 ) -> None:
     """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
@@ -1225,7 +1237,8 @@ def paged_prefill_attention(
     ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: ``prefill_cluster_size`` of the number of
     row tiles and ``cached_before``, the most tokens that a portion of this step finds in the
     cache, if the caller knows it) is the number of CTAs that share a row tile's keys in the
-    tcgen05 kernel."""
+    tcgen05 kernel.  ``chunk`` and ``softcap`` (see :func:`paged_attention_generic`) are the tcgen05
+    kernel's alone."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
     if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
         raise ValueError("q_tiles must be int32 [tiles, 4]")
@@ -1240,22 +1253,27 @@ def paged_prefill_attention(
             )
         fn = _fn(
             "einf_paged_prefill_attention_tcgen05",
-            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p],
+            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_float, c_int, c_void_p,
+                                                                 c_void_p],
             f"HEAD_SIZE={head_size}",
         )
         cluster = prefill_cluster
         if not cluster:
-            if cached_before is not None and window:
-                cached_before = min(cached_before, int(window))
+            for bound in (window, chunk):
+                if cached_before is not None and bound:
+                    cached_before = min(cached_before, int(bound))
             cluster = prefill_cluster_size(num_heads * q_tiles.shape[0], head_size, cached_before)
         _check(
             fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
                _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],
                _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1],
-               float(scale), int(window) if window else 0, int(cluster), _dev(status, "status"), _stream()),
+               float(scale), int(window) if window else 0, int(chunk) if chunk else 0,
+               float(softcap) if softcap else 0.0, int(cluster), _dev(status, "status"), _stream()),
             "paged_prefill_attention_tcgen05",
         )
         return
+    if chunk or softcap:
+        raise UnsupportedSize("a chunked mask or a soft cap needs the tcgen05 prefill kernel (head size 64 or 128)")
     fn = _fn(
         "einf_paged_prefill_attention",
         [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p],

@@ -50,10 +50,19 @@ class PagedAttention(Mixer):
             or (spec.get("value_head_size") or spec["head_size"]) != spec["head_size"]
         )
 
+    @staticmethod
+    def _general_on_tensor_cores(spec, dtype) -> bool:
+        """A general layer still runs the tcgen05 attention kernels (which know the chunked mask and
+        the soft cap) when its keys and values have one size that those kernels take."""
+        size = int(spec["head_size"])
+        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128)
+
     @classmethod
     def kernel_libraries(cls, spec, runtime):
         if cls._is_general(spec):
-            return ("pointwise", "attention_generic", "gemm_simt") + cls._product_libraries(runtime)
+            fast = (f"attention_tcgen05:HEAD_SIZE={int(spec['head_size'])}",) \
+                if cls._general_on_tensor_cores(spec, runtime.dtype) else ()
+            return ("pointwise", "attention_generic", "gemm_simt") + cls._product_libraries(runtime) + fast
         if ops.has_fast_attention(runtime.dtype, int(spec["head_size"])):
             # the page size is the engine's choice: ask for both prefill kernels of this head size
             libraries = ops.attention_libraries(int(spec["head_size"]), 16)
@@ -110,6 +119,7 @@ class PagedAttention(Mixer):
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_nested("position", spec["position"], tensors, runtime)
         self.fast = not self.general and ops.has_fast_attention(runtime.dtype, self.head_size)
+        self.general_fast = self.general and self._general_on_tensor_cores(spec, runtime.dtype)
 
     def cache_need(self):
         value = self.value_size if self.value_size != self.head_size else None
@@ -144,31 +154,35 @@ class PagedAttention(Mixer):
         """The decode attention cuts a token's keys by the number of single tokens and the bucket
         of the longest context: kernel, cluster size and clusters per token."""
         singles = int(ctx.single_tokens.shape[0])
-        if not self.fast or not singles:
+        if not (self.fast or (self.general_fast and ops.has_tcgen05_attention(self.head_size, page_size))) or not singles:
             return ()
-        context = min(ctx.max_context_len, self.window) if self.window else ctx.max_context_len
+        context = ctx.max_context_len
+        for bound in (self.window, self.chunk):
+            if bound:
+                context = min(context, bound)
         return ops.decode_plan(singles, self.num_heads, self.num_kv_heads, self.head_size, page_size, context)
 
     def launch_group(self):
         return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast, self.general)
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
-        """bfloat16 with a head size up to 128: the tensor-core kernels, cluster decode for the
+        """bfloat16 with a head size up to 128 (a layer with a chunked mask, a soft cap or unit-norm
+        heads: head sizes 64 and 128 with values as large as keys): the tensor-core kernels, cluster decode for the
         requests that bring one token, tiled prefill for the others, side by side in a mixed batch.  Everything else (the 32-bit path,
         larger heads): the generic kernel."""
         table = ctx.block_tables[cache.group]
-        if self.fast:
+        if self.fast or (self.general_fast and ops.has_tcgen05_attention(self.head_size, cache.k.shape[2])):
             singles = ctx.single_tokens.shape[0]
             if singles:
                 ops.paged_decode_attention_auto(
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
                     self.window, ctx.status, None if ctx.decode_only else ctx.single_tokens,
-                    max_context=ctx.max_context_len,
+                    max_context=ctx.max_context_len, chunk=self.chunk, softcap=self.softcap,
                 )
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(
                     q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status,
-                    cached_before=ctx.max_portion_start,
+                    cached_before=ctx.max_portion_start, chunk=self.chunk, softcap=self.softcap,
                 )
             return
         ops.paged_attention_generic(

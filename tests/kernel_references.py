@@ -171,7 +171,7 @@ def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, o
         slot = int(state_slots[r])
         if last <= first:
             continue
-        history = conv_state[slot].clone() if slot >= 0 else torch.zeros(taps - 1, x.shape[1])
+        history = conv_state[slot].clone() if slot >= 0 else torch.zeros(taps - 1, x.shape[1], device=x.device)
         line = torch.cat([history, xf[first:last]], dim=0)            # [taps - 1 + n, channels]
         for i in range(last - first):
             acc = (line[i:i + taps].T * weight).sum(dim=1)
@@ -200,7 +200,7 @@ def linear_recurrence(q, k, v, state, q_start, state_slots, y, heads, groups, di
         first, last = int(q_start[r]), int(q_start[r + 1])
         slot = int(state_slots[r])
         for h in range(heads):
-            S = state[slot, h].clone() if slot >= 0 else torch.zeros(dim, vdim)
+            S = state[slot, h].clone() if slot >= 0 else torch.zeros(dim, vdim, device=v.device)
             g = h // per_group
             for t in range(first, last):
                 a = head_decay[h] if head_decay is not None else token_decay[t, h]

@@ -67,8 +67,15 @@ CONFIGS = {
         attention(3, 3, 8, 40, 64, softcap=30.0),
         attention(3, 3, 8, 40, 3, kv_from=3),
     ], [48, None, 32, 32, 24], eps=1e-6),
+    # head sizes the tensor-core attention kernels take, chunks that are no multiple of a page
+    "wide": model(64, 83, [
+        attention(4, 2, 64, 64, 50),
+        lightning(2, 64, 64, [0.95, 0.999]),
+        mamba2(4, 32, 64, 1, 4, 1),
+        attention(4, 2, 64, 64, 33, scale=0.3, softcap=8.0, kv_from=0),
+    ], [96, 96, 96, None]),
 }
-PAGE = {"mix": 4, "ones": 8}
+PAGE = {"mix": 4, "ones": 8, "wide": 16}
 SINGLE = {
     "attention": model(32, 50, [attention(4, 2, 8, 16, 6)], [None]),
     "lightning": model(32, 50, [lightning(2, 16, 24, [0.8, 0.995])], [None]),
@@ -126,10 +133,11 @@ def replay_modes(folder, config, weights, page, dtype, device, lengths=(1, 5, 9,
     requests = make_requests(config, lengths)
     expected = expected_rows(config, weights, requests)
     mixed_steps, most = trace_tools.mixed(requests, seed=3, page_round=page)
+    room = -(-max(lengths) // 64) * 64
     traces = {
-        "whole": (trace_tools.whole(requests), 64),
-        "tail": (trace_tools.last_one_by_one(requests, tail=12), 64),
-        "portions": (trace_tools.in_portions(requests), 64),
+        "whole": (trace_tools.whole(requests), room),
+        "tail": (trace_tools.last_one_by_one(requests, tail=12), room),
+        "portions": (trace_tools.in_portions(requests), room),
         "mixed": (mixed_steps, most),
     }
     for mode, (steps, max_tokens) in traces.items():
@@ -242,6 +250,28 @@ def test_greedy_generation_through_the_entry_point_emulated(folders, emulated):
     prompts, got = generation(folder, config, weights, "float32", "cpu")
     for prompt, tokens in zip(prompts, got):
         assert tokens == greedy_plain(config, weights, prompt, 8)
+
+
+def test_command_line_runs_the_design(folders, emulated, capsys, tmp_path):
+    from einf_b200.cli.run_qwen import main
+
+    folder, config, weights = folders["mix"]
+    prompt = [5, 17, 3, 90, 4, 8, 2]
+    code = main(["--model-dir", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32",
+                 "--max-new-len", "5", "--max-prefill-chunk-len", "3", "--block-len", "4", "--max-requests", "2",
+                 "--device", "cpu", "--compare-reference"], prog="run_model")
+    out = capsys.readouterr().out
+    assert code == 0, out
+    fields = dict(line.split(": ", 1) for line in out.splitlines() if ": " in line)
+    assert json.loads(fields["generated_ids"]) == greedy_plain(config, weights, prompt, 5)
+    assert fields["tokens_equal"] == "True" and fields["completion_reason"] == "length"
+    # random weights from a bare config.json of the design
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(CONFIGS["ones"]))
+    code = main(["--random-weights", "--config", str(path), "--seed", "3", "--prompt-ids", "7,8,9", "--dtype", "float32",
+                 "--max-new-len", "4", "--block-len", "8", "--device", "cpu"])
+    out = capsys.readouterr().out
+    assert code == 0 and "generated_ids: [" in out, out
 
 
 # ---------------------------------------------------------------------------
