@@ -642,14 +642,21 @@ def tepavik_kernels(peak: dict) -> dict:
                 slots = torch.arange(requests, dtype=torch.int32, device=device)
                 decay = torch.full((r_heads,), 0.99, device=device)
 
-                def scan():
+                def scan(**how):
                     state = states[turn[0] % copies]
                     turn[0] += 1
-                    ops.linear_recurrence(qq, kk, vv, state, starts, slots, y, r_heads, groups, dim, vdim, head_decay=decay)
+                    ops.linear_recurrence(qq, kk, vv, state, starts, slots, y, r_heads, groups, dim, vdim, head_decay=decay,
+                                          max_q_len=max(lengths), **how)
 
-                us = _graph_time_us(scan, copies)
                 moved = 2 * requests * state_floats * 4 + tokens * (2 * groups * dim + r_heads * vdim) * 2 + tokens * r_heads * vdim * 4
-                rate(f"{tag}_{label}_recurrence_{what}", us, nbytes=moved, flops=4 * tokens * state_floats)
+                key = f"{tag}_{label}_recurrence_{what}"
+                rate(key, _graph_time_us(scan, copies), nbytes=moved, flops=4 * tokens * state_floats)
+                out[key + "_plan"] = list(ops.recurrence_plan(requests, max(lengths), r_heads, dim, vdim))
+                if tokens > requests:     # a prompt: the same in one segment, and with every number of rows per thread
+                    for rows in (4, 8, 16):
+                        out[f"{key}_one_segment_rows{rows}_us"] = round(_graph_time_us(
+                            lambda: scan(rows=rows, segment_len=tokens), copies), 1)
+                        out[f"{key}_segments_rows{rows}_us"] = round(_graph_time_us(lambda: scan(rows=rows), copies), 1)
     out["status"] = int(status)
     return out
 

@@ -6,6 +6,8 @@
 // zeros and writes nothing.  The step's tokens are packed request by request, q_start[r] ..
 // q_start[r + 1], so a prompt portion and a single decoded token take the same code and the same
 // order of additions: what a position computes does not depend on how the prompt was cut.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace einf {
@@ -99,14 +101,42 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long in_
 // groups).  With `act` the inputs pass SiLU as they are read.  q, k, v are rows of some wider
 // matrix: element (t, head, i) of q is q[t * q_stride + head * dim + i].
 //
-// A thread owns kRows consecutive rows of one column of S; the 2^n lanes that share a column
-// (lanes_per_column >= dim / kRows) sit kColumns apart in a warp so that loads and stores of S are
-// contiguous over the columns, and add their parts of y with shuffles.  Tokens are taken one
-// after the other: the order of the additions is the same for a whole prompt, for portions and
-// for single tokens.
+// A thread owns ROWS consecutive rows of one column of S; the 2^n lanes that share a column
+// (lanes_per_column = dim_pad / ROWS) sit columns_per_warp apart in a warp, so that loads and
+// stores of S are contiguous over the columns, and add their parts of y with shuffles.  The CTA
+// brings the inputs of a batch of tokens into shared memory as floats, activated once (every
+// column needs the same k_t and q_t), while it works on the batch before; tokens are then taken
+// one after the other.
+//
+// A long portion is cut into segments of `segment_len` tokens that run side by side (a single
+// request's prompt would otherwise keep a few warps busy, each waiting on itself): a first pass
+// adds up every segment's own contribution B from a zero state together with the product P of
+// its decays, a small kernel walks the segments (S_start of the next = P S_start + B) and writes
+// the request's final state, and the emitting pass runs every segment from its start state.
+// Portions of up to segment_len tokens (decoding among them) take the emitting pass alone, which
+// then reads and writes the slot itself.
 // ---------------------------------------------------------------------------
-constexpr int kRows = 16;
+// Shared memory by its own instructions: the staged inputs are read once per token by every thread.
+// (volatile keeps them in order among themselves and with the barriers; no memory clobber, so that
+// the arithmetic of one token may be scheduled around the loads of the next.)
+__device__ __forceinline__ float4 lds128(uint32_t address) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ float lds32(uint32_t address) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t address, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+
 constexpr int kRecurrenceThreads = 128;
+constexpr int kStageKQ = 8;      // k (and q) elements a thread stages per batch: batch * dim <= 8 * 128
+constexpr int kStageV = 4;       // v elements a thread stages per batch: batch * columns of the CTA <= 4 * 128
+constexpr int kMaxBatch = 16;
 
 struct RecurrenceArgs {
   const void* q; const void* k; const void* v;
@@ -115,99 +145,236 @@ struct RecurrenceArgs {
   float* state; long long state_stride;
   const int* q_start; const int* state_slots;
   float* y;
-  int num_slots, heads, groups, dim, vdim, act, lanes_per_column, vector_loads;
+  float* segment_state;    // [requests * segments, heads, dim, vdim]: B after the first pass, start states after the walk
+  float* segment_decay;    // [requests * segments, heads]
+  int num_slots, heads, groups, dim, vdim, act, lanes_per_column, dim_pad, batch, segments, segment_len;
 };
 
-template <typename T>
-__device__ __forceinline__ void load_rows(const T* __restrict__ p, int r0, int dim, bool vectors, bool act,
-                                          float (&out)[kRows]) {
-  if (vectors && r0 + kRows <= dim) {
-    constexpr int kPerVec = 16 / sizeof(T);
-#pragma unroll
-    for (int i = 0; i < kRows; i += kPerVec) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(p + r0 + i);
-      const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-      for (int u = 0; u < kPerVec; ++u) out[i + u] = to_float(e[u]);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) out[i] = (r0 + i < dim) ? to_float(p[r0 + i]) : 0.f;
-  }
-  if (act) {
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) out[i] = silu_f(out[i]);
-  }
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kRecurrenceThreads)
-linear_recurrence_kernel(const RecurrenceArgs a) {
+// kEmit false: the first pass (no queries, no output, state from zero into segment_state).
+template <typename T, int ROWS, bool kEmit>
+__global__ void __launch_bounds__(kRecurrenceThreads, 4)
+linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int lanes = a.lanes_per_column;          // a power of two, 1 .. 32
   const int columns_per_warp = 32 / lanes;
+  const int columns_per_block = (kRecurrenceThreads / 32) * columns_per_warp;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / columns_per_warp;       // which rows of the column
-  const int column = (blockIdx.x * (kRecurrenceThreads / 32) + warp) * columns_per_warp + (lane % columns_per_warp);
-  const int head = blockIdx.y, r = blockIdx.z;
+  const int local_column = warp * columns_per_warp + (lane % columns_per_warp);
+  const int column0 = blockIdx.x * columns_per_block;
+  const int head = blockIdx.y;
+  const int r = blockIdx.z / a.segments, segment = blockIdx.z - r * a.segments;
   const int group = head / (a.heads / a.groups);
-  const int first = a.q_start[r], last = a.q_start[r + 1];
+  const int request_first = a.q_start[r], request_last = a.q_start[r + 1];
+  const int count = request_last - request_first;
+  const int num_segments = (count + a.segment_len - 1) / a.segment_len;
+  if (segment >= num_segments || (!kEmit && num_segments <= 1)) return;
+  const int first = request_first + segment * a.segment_len;
+  const int last = min(request_last, first + a.segment_len);
   const int slot = a.state_slots[r];
-  const bool live = column < a.vdim;
-  const int col = live ? column : a.vdim - 1;     // idle lanes follow along and write nothing
-  const int r0 = part * kRows;
-  const bool vectors = a.vector_loads != 0;
-  const bool act = a.act != 0;
+  const bool live = column0 + local_column < a.vdim;
+  const int col = live ? column0 + local_column : a.vdim - 1;     // idle lanes follow along and write nothing
+  const int r0 = part * ROWS;
+  const int dim = a.dim, dim_pad = a.dim_pad, batch = a.batch;
 
-  float* state = (slot >= 0 && slot < a.num_slots)
-      ? a.state + (long long)slot * a.state_stride + ((long long)head * a.dim) * a.vdim + col : nullptr;
-  float S[kRows];
+  // shared memory: two buffers of [k: batch x dim_pad | q: batch x dim_pad | v: batch x columns | a: batch | s: batch]
+  const int kq_floats = batch * dim_pad;
+  const int buffer_floats = ((kEmit ? 2 : 1) * kq_floats + batch * columns_per_block + 2 * batch + 3) & ~3;
+  for (int i = threadIdx.x; i < 2 * buffer_floats; i += kRecurrenceThreads) smem[i] = 0.f;   // rows beyond dim stay zero
+
+  const float* start_state = nullptr;
+  float* end_state = nullptr;
+  const long long in_head = ((long long)head * dim) * a.vdim + col;
+  if (kEmit) {
+    if (num_segments == 1) {
+      if (slot >= 0 && slot < a.num_slots) start_state = a.state + (long long)slot * a.state_stride + in_head;
+    } else {
+      // the walk over the segments left every segment's start state there (the first one's too:
+      // the slot itself already holds the request's final state)
+      start_state = a.segment_state + ((long long)blockIdx.z * a.heads * dim) * a.vdim + in_head;
+    }
+    if (num_segments == 1 && slot >= 0 && slot < a.num_slots) end_state = a.state + (long long)slot * a.state_stride + in_head;
+  } else {
+    end_state = a.segment_state + ((long long)blockIdx.z * a.heads * dim) * a.vdim + in_head;
+  }
+  float S[ROWS];
 #pragma unroll
-  for (int i = 0; i < kRows; ++i) S[i] = (state && r0 + i < a.dim) ? state[(long long)(r0 + i) * a.vdim] : 0.f;
+  for (int i = 0; i < ROWS; ++i) S[i] = (start_state && r0 + i < dim) ? start_state[(long long)(r0 + i) * a.vdim] : 0.f;
 
-  const T* q = (const T*)a.q + (long long)group * a.dim;
-  const T* k = (const T*)a.k + (long long)group * a.dim;
-  const T* v = (const T*)a.v + (long long)head * a.vdim + col;
+  const T* qg = (const T*)a.q + (long long)group * dim;
+  const T* kg = (const T*)a.k + (long long)group * dim;
+  const T* vg = (const T*)a.v + (long long)head * a.vdim + column0;
   const float constant_decay = a.head_decay ? a.head_decay[head] : 1.f;
   const float skip = a.skip ? a.skip[head] : 0.f;
+  const bool act = a.act != 0;
+  const long long k_stride = a.k_stride, q_stride = a.q_stride, v_stride = a.v_stride;
+  const float* token_decay = a.token_decay;
+  const float* token_scale = a.token_scale;
+  const int heads = a.heads;
 
-  float kn[kRows], qn[kRows], vn = 0.f, an = constant_decay, sn = 1.f;
-  if (first < last) {
-    load_rows(k + (long long)first * a.k_stride, r0, a.dim, vectors, act, kn);
-    load_rows(q + (long long)first * a.q_stride, r0, a.dim, vectors, act, qn);
-    vn = to_float(v[(long long)first * a.v_stride]);
-    if (act) vn = silu_f(vn);
-    if (a.token_decay) an = a.token_decay[(long long)first * a.heads + head];
-    if (a.token_scale) sn = a.token_scale[(long long)first * a.heads + head];
+  // What this thread stages of a batch: element idx = threadIdx.x + j * 128 of [batch x dim] (k and q) and of
+  // [batch x columns] (v); token and index inside the token, packed, -1 for none.
+  int kq_where[kStageKQ], v_where[kStageV];
+#pragma unroll
+  for (int j = 0; j < kStageKQ; ++j) {
+    const int idx = threadIdx.x + j * kRecurrenceThreads;
+    const int tt = idx / dim;
+    kq_where[j] = tt < batch ? (tt << 16) | (idx - tt * dim) : -1;
   }
-  for (int t = first; t < last; ++t) {
-    float kc[kRows], qc[kRows];
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) { kc[i] = kn[i]; qc[i] = qn[i]; }
-    const float vc = vn, ac = an, sc = sn;
-    if (t + 1 < last) {      // the next token's inputs are on their way while this one is added
-      load_rows(k + (long long)(t + 1) * a.k_stride, r0, a.dim, vectors, act, kn);
-      load_rows(q + (long long)(t + 1) * a.q_stride, r0, a.dim, vectors, act, qn);
-      vn = to_float(v[(long long)(t + 1) * a.v_stride]);
-      if (act) vn = silu_f(vn);
-      if (a.token_decay) an = a.token_decay[(long long)(t + 1) * a.heads + head];
-      if (a.token_scale) sn = a.token_scale[(long long)(t + 1) * a.heads + head];
-    }
-    const float sv = sc * vc;
-    float y = 0.f;
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      S[i] = fmaf(ac, S[i], kc[i] * sv);
-      y = fmaf(S[i], qc[i], y);
-    }
-    for (int o = columns_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-    if (live && part == 0) a.y[((long long)t * a.heads + head) * a.vdim + col] = y + skip * vc;
+  for (int j = 0; j < kStageV; ++j) {
+    const int idx = threadIdx.x + j * kRecurrenceThreads;
+    const int tt = idx / columns_per_block;
+    const int c = idx - tt * columns_per_block;
+    v_where[j] = (tt < batch && column0 + c < a.vdim) ? (tt << 16) | c : -1;
   }
-  if (state && live && first < last) {
+  // staged as they come (converted when they are put into shared memory: a conversion right behind
+  // its load would make the warp wait for the load before it starts on the batch at hand)
+  T k_regs[kStageKQ], q_regs[kStageKQ], v_regs[kStageV];
+  float a_reg = constant_decay, s_reg = 1.f;
+  const T zero = from_float<T>(0.f);
+  auto fetch = [&](int t0) {
+    const int n = min(batch, last - t0);
 #pragma unroll
-    for (int i = 0; i < kRows; ++i)
-      if (r0 + i < a.dim) state[(long long)(r0 + i) * a.vdim] = S[i];
+    for (int j = 0; j < kStageKQ; ++j) {
+      const int tt = kq_where[j] >> 16, i = kq_where[j] & 0xffff;
+      const bool valid = kq_where[j] >= 0 && tt < n;
+      k_regs[j] = valid ? kg[(long long)(t0 + tt) * k_stride + i] : zero;
+      if (kEmit) q_regs[j] = valid ? qg[(long long)(t0 + tt) * q_stride + i] : zero;
+    }
+#pragma unroll
+    for (int j = 0; j < kStageV; ++j) {
+      const int tt = v_where[j] >> 16, c = v_where[j] & 0xffff;
+      v_regs[j] = (v_where[j] >= 0 && tt < n) ? vg[(long long)(t0 + tt) * v_stride + c] : zero;
+    }
+    if (threadIdx.x < n) {
+      if (token_decay) a_reg = token_decay[(long long)(t0 + threadIdx.x) * heads + head];
+      if (token_scale) s_reg = token_scale[(long long)(t0 + threadIdx.x) * heads + head];
+    }
+  };
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int v_offset = (kEmit ? 2 : 1) * kq_floats;             // floats from a buffer's start
+  const int a_offset = v_offset + batch * columns_per_block;
+  auto stash = [&](uint32_t buffer) {                           // buffer: shared address of the buffer's start
+#pragma unroll
+    for (int j = 0; j < kStageKQ; ++j) {
+      if (kq_where[j] < 0) continue;
+      const uint32_t at = buffer + 4u * ((kq_where[j] >> 16) * dim_pad + (kq_where[j] & 0xffff));
+      sts32(at, act ? silu_f(to_float(k_regs[j])) : to_float(k_regs[j]));
+      if (kEmit) sts32(at + 4u * kq_floats, act ? silu_f(to_float(q_regs[j])) : to_float(q_regs[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < kStageV; ++j) {
+      if (v_where[j] < 0) continue;
+      sts32(buffer + 4u * (v_offset + (v_where[j] >> 16) * columns_per_block + (v_where[j] & 0xffff)),
+            act ? silu_f(to_float(v_regs[j])) : to_float(v_regs[j]));
+    }
+    if (threadIdx.x < batch) {
+      sts32(buffer + 4u * (a_offset + threadIdx.x), a_reg);
+      sts32(buffer + 4u * (a_offset + batch + threadIdx.x), s_reg);
+    }
+  };
+
+  __syncthreads();                 // the zeros are in place
+  fetch(first);
+  stash(smem_base);
+  __syncthreads();
+  float decay_product = 1.f;
+  int turn = 0;
+  float* y_out = a.y + ((long long)first * a.heads + head) * a.vdim + col;
+  const long long y_step = (long long)a.heads * a.vdim;
+  for (int t0 = first; t0 < last; t0 += batch, turn ^= 1) {
+    const uint32_t buffer = smem_base + 4u * (turn * buffer_floats);
+    const bool more = t0 + batch < last;
+    if (more) fetch(t0 + batch);   // on its way while this batch is added
+    const uint32_t kb = buffer + 4u * r0;
+    const uint32_t qb = kb + 4u * kq_floats;
+    const uint32_t vb = buffer + 4u * (v_offset + local_column);
+    const uint32_t ab = buffer + 4u * a_offset;
+    const int n = min(batch, last - t0);
+    // kTokens tokens in a row: the state is updated token after token, the lanes' parts of the kTokens
+    // outputs are added across the lanes together (shuffles of different tokens overlap).
+    auto tokens = [&](int tt, auto count_tag) {
+      constexpr int kTokens = decltype(count_tag)::value;
+      float yp[kTokens], vcs[kTokens];
+#pragma unroll
+      for (int u = 0; u < kTokens; ++u) {
+        const float ac = lds32(ab + 4u * (tt + u)), vc = lds32(vb + 4u * ((tt + u) * columns_per_block));
+        const float sv = lds32(ab + 4u * (batch + tt + u)) * vc;
+        float4 kc[ROWS / 4], qc[ROWS / 4];
+#pragma unroll
+        for (int i = 0; i < ROWS / 4; ++i) {
+          kc[i] = lds128(kb + 4u * ((tt + u) * dim_pad + 4 * i));
+          if (kEmit) qc[i] = lds128(qb + 4u * ((tt + u) * dim_pad + 4 * i));
+        }
+        float y4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < ROWS / 4; ++i) {
+          S[4 * i + 0] = fmaf(ac, S[4 * i + 0], kc[i].x * sv);
+          S[4 * i + 1] = fmaf(ac, S[4 * i + 1], kc[i].y * sv);
+          S[4 * i + 2] = fmaf(ac, S[4 * i + 2], kc[i].z * sv);
+          S[4 * i + 3] = fmaf(ac, S[4 * i + 3], kc[i].w * sv);
+          if (kEmit) {
+            y4[0] = fmaf(S[4 * i + 0], qc[i].x, y4[0]);
+            y4[1] = fmaf(S[4 * i + 1], qc[i].y, y4[1]);
+            y4[2] = fmaf(S[4 * i + 2], qc[i].z, y4[2]);
+            y4[3] = fmaf(S[4 * i + 3], qc[i].w, y4[3]);
+          }
+        }
+        yp[u] = (y4[0] + y4[1]) + (y4[2] + y4[3]);
+        vcs[u] = vc;
+        if (!kEmit) decay_product *= ac;
+      }
+      if (kEmit) {
+        for (int o = columns_per_warp; o < 32; o <<= 1) {
+#pragma unroll
+          for (int u = 0; u < kTokens; ++u) yp[u] += __shfl_xor_sync(0xffffffffu, yp[u], o);
+        }
+        if (live && part == 0) {
+#pragma unroll
+          for (int u = 0; u < kTokens; ++u) y_out[u * y_step] = yp[u] + skip * vcs[u];
+        }
+        y_out += kTokens * y_step;
+      }
+    };
+    int tt = 0;
+    for (; tt + 4 <= n; tt += 4) tokens(tt, std::integral_constant<int, 4>{});
+    for (; tt < n; ++tt) tokens(tt, std::integral_constant<int, 1>{});
+    if (more) stash(smem_base + 4u * ((turn ^ 1) * buffer_floats));
+    __syncthreads();
+  }
+  if (end_state && live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+      if (r0 + i < dim) end_state[(long long)(r0 + i) * a.vdim] = S[i];
+  }
+  if (!kEmit && blockIdx.x == 0 && threadIdx.x == 0) a.segment_decay[(long long)blockIdx.z * a.heads + head] = decay_product;
+}
+
+// Between the two passes: walk a request's segments, S_start(next) = P S_start + B, leave every
+// segment's start state where its B was, and write the request's final state into its slot.
+__global__ void recurrence_walk_kernel(const __grid_constant__ RecurrenceArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.y, r = blockIdx.z;
+  const int count = a.q_start[r + 1] - a.q_start[r];
+  const int num_segments = (count + a.segment_len - 1) / a.segment_len;
+  if (num_segments <= 1) return;
+  const int slot = a.state_slots[r];
+  const long long per_head = (long long)a.dim * a.vdim;
+  float* slot_state = (slot >= 0 && slot < a.num_slots) ? a.state + (long long)slot * a.state_stride + head * per_head : nullptr;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < per_head; e += (long long)gridDim.x * blockDim.x) {
+    float current = slot_state ? slot_state[e] : 0.f;
+    for (int segment = 0; segment < num_segments; ++segment) {
+      const long long index = (long long)r * a.segments + segment;
+      float* at = a.segment_state + (index * a.heads + head) * per_head + e;
+      const float b = *at;
+      *at = current;
+      current = fmaf(a.segment_decay[index * a.heads + head], current, b);
+    }
+    if (slot_state) slot_state[e] = current;
   }
 }
 
@@ -277,16 +444,25 @@ extern "C" int einf_conv_silu(const void* in, int dtype, long long in_stride, co
   })
 }
 
+// rows per thread: 0 lets the launcher choose among 16, 8 and 4.  segments > 1 needs segment_state [requests * segments,
+// heads, dim, vdim] and segment_decay [requests * segments, heads].
 extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* v, int dtype, long long q_stride,
                                       long long k_stride, long long v_stride, const float* head_decay,
                                       const float* token_decay, const float* token_scale, const float* skip,
                                       float* state, long long state_stride, int num_slots, const int* q_start,
                                       const int* state_slots, int num_requests, float* y, int heads, int groups,
-                                      int dim, int vdim, int act, cudaStream_t stream) {
+                                      int dim, int vdim, int act, int rows, int segments, int segment_len,
+                                      float* segment_state, float* segment_decay, cudaStream_t stream) {
   if (num_requests == 0) return 0;
-  if (heads <= 0 || groups <= 0 || heads % groups || dim <= 0 || vdim <= 0 || dim > 32 * kRows ||
-      heads > 65535 || num_requests > 65535)
+  if (heads <= 0 || groups <= 0 || heads % groups || dim <= 0 || vdim <= 0 || dim > 512 || heads > 65535 ||
+      segments < 1 || segment_len < 1 || (long long)num_requests * segments > 65535 ||
+      (segments > 1 && (!segment_state || !segment_decay)))
     return (int)cudaErrorInvalidValue;
+  // Sixteen rows a thread wherever the state has that many: measured at every size tried (14 heads of
+  // 64 x 64 and of 128 x 64, 12 of 128 x 128; one segment and sixteen), fewer rows, which are more and
+  // lighter threads, were slower.
+  if (rows == 0) rows = dim > 8 ? 16 : dim > 4 ? 8 : 4;
+  if ((rows != 4 && rows != 8 && rows != 16) || 32 * rows < dim) return (int)cudaErrorInvalidValue;
   RecurrenceArgs a;
   a.q = q; a.k = k; a.v = v;
   a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
@@ -294,19 +470,44 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
   a.state = state; a.state_stride = state_stride;
   a.q_start = q_start; a.state_slots = state_slots;
   a.y = y;
+  a.segment_state = segment_state; a.segment_decay = segment_decay;
   a.num_slots = num_slots; a.heads = heads; a.groups = groups; a.dim = dim; a.vdim = vdim; a.act = act;
+  a.segments = segments; a.segment_len = segment_len;
   int lanes = 1;
-  while (lanes * kRows < dim) lanes <<= 1;
+  while (lanes * rows < dim) lanes <<= 1;
   a.lanes_per_column = lanes;
-  const int element = dtype == kFloat32 ? 4 : 2;
-  const int per_vector = 16 / element;
-  a.vector_loads = (dim % per_vector == 0 && q_stride % per_vector == 0 && k_stride % per_vector == 0 &&
-                    ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0) ? 1 : 0;
+  a.dim_pad = lanes * rows;
   const int columns_per_block = (kRecurrenceThreads / 32) * (32 / lanes);
-  const dim3 grid((vdim + columns_per_block - 1) / columns_per_block, heads, num_requests);
+  int batch = kStageKQ * kRecurrenceThreads / dim;
+  if (batch > kStageV * kRecurrenceThreads / columns_per_block) batch = kStageV * kRecurrenceThreads / columns_per_block;
+  if (batch > kMaxBatch) batch = kMaxBatch;
+  if (batch < 1) return (int)cudaErrorInvalidValue;
+  a.batch = batch;
+  const dim3 grid((vdim + columns_per_block - 1) / columns_per_block, heads, num_requests * segments);
+  auto buffer_bytes = [&](bool emit) {
+    const int floats = ((emit ? 2 : 1) * batch * a.dim_pad + batch * columns_per_block + 2 * batch + 3) & ~3;
+    return (size_t)2 * floats * sizeof(float);
+  };
+#define EINF_RECURRENCE_ROWS(ROWS_)                                                                                   \
+  {                                                                                                                   \
+    if (segments > 1) {                                                                                               \
+      cudaError_t e = launch_pdl(linear_recurrence_kernel<T, ROWS_, false>, grid, kRecurrenceThreads,                 \
+                                 buffer_bytes(false), stream, a);                                                     \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+      const long long per_head = (long long)dim * vdim;                                                               \
+      const dim3 walk_grid((unsigned)((per_head + 255) / 256 > 64 ? 64 : (per_head + 255) / 256), heads, num_requests); \
+      e = launch_pdl(recurrence_walk_kernel, walk_grid, 256, 0, stream, a);                                           \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    return (int)launch_pdl(linear_recurrence_kernel<T, ROWS_, true>, grid, kRecurrenceThreads, buffer_bytes(true),   \
+                           stream, a);                                                                                \
+  }
   EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(linear_recurrence_kernel<T>, grid, kRecurrenceThreads, 0, stream, a);
+    if (rows == 16) EINF_RECURRENCE_ROWS(16)
+    if (rows == 8) EINF_RECURRENCE_ROWS(8)
+    EINF_RECURRENCE_ROWS(4)
   })
+#undef EINF_RECURRENCE_ROWS
 }
 
 extern "C" int einf_gated_norm(const float* y, const void* gate, int dtype, long long gate_stride, const float* weight,

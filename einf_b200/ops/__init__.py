@@ -698,6 +698,32 @@ def conv_silu(
     )
 
 
+#: tokens of a segment when a long portion is cut so that its segments run side by side
+SEGMENT_TOKENS = 128
+#: most segments of one request
+MAX_SEGMENTS = 64
+
+
+def recurrence_plan(num_requests: int, max_q_len: Optional[int], heads: int, dim: int, vdim: int,
+                    sms: Optional[int] = None) -> tuple[int, int]:
+    """``(segments, segment_len)`` of a recurrence launch: portions longer than ``SEGMENT_TOKENS`` are
+    cut into segments that run side by side (at one and a half times the arithmetic) when the
+    requests and heads alone would leave most of the GPU's schedulers without a warp."""
+    if not max_q_len or max_q_len <= SEGMENT_TOKENS:
+        return 1, max(1, max_q_len or 1)
+    lanes = 1
+    while lanes * 16 < dim:
+        lanes *= 2
+    warps = num_requests * heads * vdim * lanes // 32
+    if warps >= (sms or _sm_count()) * 16:
+        return 1, max_q_len
+    limit = max(1, min(MAX_SEGMENTS, 65535 // max(1, num_requests)))
+    segment_len = SEGMENT_TOKENS
+    if -(-max_q_len // segment_len) > limit:
+        segment_len = -(-(-(-max_q_len // limit)) // 16) * 16
+    return -(-max_q_len // segment_len), segment_len
+
+
 def linear_recurrence(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -715,6 +741,9 @@ def linear_recurrence(
     token_scale: Optional[torch.Tensor] = None,
     skip: Optional[torch.Tensor] = None,
     silu_inputs: bool = False,
+    max_q_len: Optional[int] = None,
+    rows: int = 0,
+    segment_len: Optional[int] = None,
 ) -> None:
     """Per request and head, over its tokens in order, with a float32 state ``S [dim, vdim]``::
 
@@ -726,7 +755,9 @@ def linear_recurrence(
     heads]`` or 1; ``skip [heads]`` or 0; all float32.  ``silu_inputs``: q, k and v pass SiLU as
     they are read.  ``state [slots, heads, dim, vdim]`` float32 (slot stride may be larger) is read
     at the start of each request's portion and written at its end; ``y [tokens, heads * vdim]``
-    float32."""
+    float32.  ``max_q_len`` is the longest portion of the step as the host knows it (None: unknown,
+    no portion is cut into segments); ``rows`` (0, 4, 8, 16) and ``segment_len`` override the
+    launch's own choices (:func:`recurrence_plan`), for tests and measurements."""
     tokens = v.shape[0]
     if q.shape != (tokens, groups * dim) or k.shape != q.shape or v.shape != (tokens, heads * vdim):
         raise ValueError(f"q, k must be [{tokens}, {groups * dim}] and v [{tokens}, {heads * vdim}]")
@@ -747,21 +778,40 @@ def linear_recurrence(
                            ("token_scale", token_scale, (tokens, heads)), ("skip", skip, (heads,))):
         if t is not None and (t.dtype != torch.float32 or t.shape != shape or not t.is_contiguous()):
             raise ValueError(f"{name} must be contiguous float32 {shape}")
+    requests = state_slots.shape[0]
+    if tokens == 0 or requests == 0:
+        return
+    if segment_len is not None:
+        longest = max_q_len or tokens
+        segments, segment_len = -(-longest // int(segment_len)), int(segment_len)
+    else:
+        segments, segment_len = recurrence_plan(requests, max_q_len, heads, dim, vdim)
+        if max_q_len is None:
+            segment_len = tokens
+    segment_state = segment_decay = None
+    if segments > 1:
+        segment_state = torch.empty((requests * segments, heads, dim, vdim), dtype=torch.float32, device=y.device)
+        segment_decay = torch.empty((requests * segments, heads), dtype=torch.float32, device=y.device)
     fn = _fn(
         "einf_linear_recurrence",
         [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-         c_int, c_void_p],
+         c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     )
     _check(
         fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), _code(q), _rows_of(q, "q"), _rows_of(k, "k"), _rows_of(v, "v"),
            _opt(head_decay, "head_decay", torch.float32), _opt(token_decay, "token_decay", torch.float32),
            _opt(token_scale, "token_scale", torch.float32), _opt(skip, "skip", torch.float32),
            state.data_ptr(), state.stride(0), state.shape[0], _opt(q_start, "q_start", torch.int32),
-           _opt(state_slots, "state_slots", torch.int32), state_slots.shape[0], _dev(y, "y"), heads, groups, dim,
-           vdim, 1 if silu_inputs else 0, _stream()),
+           _opt(state_slots, "state_slots", torch.int32), requests, _dev(y, "y"), heads, groups, dim,
+           vdim, 1 if silu_inputs else 0, int(rows), segments, segment_len,
+           _opt(segment_state, "segment_state", torch.float32), _opt(segment_decay, "segment_decay", torch.float32),
+           _stream()),
         "linear_recurrence",
     )
+    if segments > 1:
+        global launch_count
+        launch_count += 2      # the first pass and the walk over the segments
 
 
 def gated_norm(

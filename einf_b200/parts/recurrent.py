@@ -34,6 +34,16 @@ class _RecurrentMixer(Mixer):
             ("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()
         )
 
+    #: (heads, rows, columns) of the recurrent state, set by the subclasses
+    state_shape: tuple[int, int, int] = (0, 0, 0)
+
+    def launch_key(self, ctx: StepContext, page_size: int) -> tuple:
+        """Long portions are cut into segments by the step's longest portion, a host-side figure."""
+        return ops.recurrence_plan(ctx.num_requests, ctx.max_q_len, *self.state_shape)
+
+    def launch_group(self):
+        return ("recurrence",) + self.state_shape
+
     def _state(self, cache: CacheView) -> torch.Tensor:
         if cache.state is None or not cache.writes:
             raise ValueError(f"a {self.kind} mixer needs a state of its own")
@@ -72,6 +82,7 @@ class LightningAttention(_RecurrentMixer):
         self.in_weight = runtime.matrix(torch.cat(matrices, dim=0))
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
         self.norm_weight = runtime.vector(tensors["norm.weight"])
+        self.state_shape = (self.heads, self.dim, self.vdim)
 
     def cache_need(self):
         return StateNeed((self.heads * self.dim * self.vdim,), torch.float32)
@@ -87,6 +98,7 @@ class LightningAttention(_RecurrentMixer):
         ops.linear_recurrence(
             q, k, v, state.view(state.shape[0], self.heads, self.dim, self.vdim), ctx.q_start, ctx.state_slots, y,
             self.heads, self.heads, self.dim, self.vdim, head_decay=self.decay, silu_inputs=True,
+            max_q_len=ctx.max_q_len,
         )
         out = torch.empty((tokens, values), dtype=self.runtime.dtype, device=x.device)
         ops.gated_norm(y, gate, self.norm_weight, out, 1, self.eps, gate_first=False, gate_kind="sigmoid")
@@ -139,6 +151,7 @@ class Mamba2(_RecurrentMixer):
         self.skip = runtime.vector(tensors["D"])
         self.norm_weight = runtime.vector(tensors["norm.weight"])
         self.state_floats = self.heads * self.state_size * self.vdim
+        self.state_shape = (self.heads, self.state_size, self.vdim)
 
     def cache_need(self):
         # the recurrent state, then the convolution's last taps-1 inputs [taps-1, channels]
@@ -165,7 +178,7 @@ class Mamba2(_RecurrentMixer):
         y = torch.empty((tokens, inner), dtype=torch.float32, device=device)
         ops.linear_recurrence(
             c, b, xs, recurrent, ctx.q_start, ctx.state_slots, y, heads, self.groups, self.state_size, self.vdim,
-            token_decay=decay, token_scale=dt, skip=self.skip,
+            token_decay=decay, token_scale=dt, skip=self.skip, max_q_len=ctx.max_q_len,
         )
         out = torch.empty((tokens, inner), dtype=self.runtime.dtype, device=device)
         ops.gated_norm(y, z, self.norm_weight, out, self.norm_groups, self.eps, gate_first=True, gate_kind="silu")

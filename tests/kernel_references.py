@@ -187,7 +187,8 @@ def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, o
 
 
 def linear_recurrence(q, k, v, state, q_start, state_slots, y, heads, groups, dim, vdim, head_decay=None,
-                      token_decay=None, token_scale=None, skip=None, silu_inputs=False):
+                      token_decay=None, token_scale=None, skip=None, silu_inputs=False, max_q_len=None, rows=0,
+                      segment_len=None):
     def act(t):
         t = t.float()
         return t / (1 + torch.exp(-t)) if silu_inputs else t
@@ -311,11 +312,15 @@ def ensure_built(names):
     return None
 
 
+def recurrence_plan(num_requests, max_q_len, heads, dim, vdim, sms=None):
+    return 1, max(1, max_q_len or 1)
+
+
 _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
-    "gated_norm",
+    "gated_norm", "recurrence_plan",
 )
 
 
