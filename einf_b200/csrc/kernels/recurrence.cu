@@ -378,6 +378,83 @@ __global__ void recurrence_walk_kernel(const __grid_constant__ RecurrenceArgs a)
   }
 }
 
+// One token per request (a decode step): the state is streamed through once, four columns a
+// thread with 16-byte loads and stores along the rows, S <- a S + k (s v)^T and the thread's part of
+// y = S^T q in the same pass; the row groups' parts of y meet in shared memory.  vdim / 4 must
+// divide the 128 threads (the launcher sends other sizes to the kernel above).
+template <typename T>
+__global__ void __launch_bounds__(kRecurrenceThreads)
+recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.x, r = blockIdx.y;
+  const int t = a.q_start[r];
+  if (a.q_start[r + 1] - t != 1) return;
+  const int dim = a.dim, vdim = a.vdim;
+  const int slot = a.state_slots[r];
+  const int group = head / (a.heads / a.groups);
+  float* ks = smem;                    // [dim]
+  float* qs = ks + dim;                // [dim]
+  float* vs = qs + dim;                // [vdim], already times s_t
+  float* parts = vs + vdim;            // [row groups][vdim]
+  const bool act = a.act != 0;
+  const T* kg = (const T*)a.k + (long long)t * a.k_stride + (long long)group * dim;
+  const T* qg = (const T*)a.q + (long long)t * a.q_stride + (long long)group * dim;
+  const T* vg = (const T*)a.v + (long long)t * a.v_stride + (long long)head * vdim;
+  const float decay = a.token_decay ? a.token_decay[(long long)t * a.heads + head] : a.head_decay[head];
+  const float scale = a.token_scale ? a.token_scale[(long long)t * a.heads + head] : 1.f;
+  for (int i = threadIdx.x; i < dim; i += kRecurrenceThreads) {
+    const float kv = to_float(kg[i]), qv = to_float(qg[i]);
+    ks[i] = act ? silu_f(kv) : kv;
+    qs[i] = act ? silu_f(qv) : qv;
+  }
+  for (int i = threadIdx.x; i < vdim; i += kRecurrenceThreads) {
+    const float v = to_float(vg[i]);
+    vs[i] = scale * (act ? silu_f(v) : v);
+  }
+  __syncthreads();
+  const int quads = vdim >> 2;                       // divides 128
+  const int cq = threadIdx.x % quads, row0 = threadIdx.x / quads, row_step = kRecurrenceThreads / quads;
+  const float4 sv = *reinterpret_cast<const float4*>(vs + 4 * cq);
+  float4* state = (slot >= 0 && slot < a.num_slots)
+      ? reinterpret_cast<float4*>(a.state + (long long)slot * a.state_stride + ((long long)head * dim) * vdim) + cq : nullptr;
+  float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+  constexpr int kInFlight = 8;
+  for (int row = row0; row < dim; row += row_step * kInFlight) {
+    float4 s[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int rr = row + u * row_step;
+      s[u] = (state && rr < dim) ? state[(long long)rr * quads] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int rr = row + u * row_step;
+      if (rr >= dim) break;
+      const float kv = ks[rr], qv = qs[rr];
+      s[u].x = fmaf(decay, s[u].x, kv * sv.x);
+      s[u].y = fmaf(decay, s[u].y, kv * sv.y);
+      s[u].z = fmaf(decay, s[u].z, kv * sv.z);
+      s[u].w = fmaf(decay, s[u].w, kv * sv.w);
+      y.x = fmaf(s[u].x, qv, y.x);
+      y.y = fmaf(s[u].y, qv, y.y);
+      y.z = fmaf(s[u].z, qv, y.z);
+      y.w = fmaf(s[u].w, qv, y.w);
+      if (state) state[(long long)rr * quads] = s[u];
+    }
+  }
+  *reinterpret_cast<float4*>(parts + row0 * vdim + 4 * cq) = y;
+  __syncthreads();
+  const float skip = a.skip ? a.skip[head] : 0.f;
+  for (int c = threadIdx.x; c < vdim; c += kRecurrenceThreads) {
+    float total = 0.f;
+    for (int g = 0; g < row_step; ++g) total += parts[g * vdim + c];
+    const float v = to_float(vg[c]);
+    a.y[((long long)t * a.heads + head) * vdim + c] = total + skip * (act ? silu_f(v) : v);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Gate and norm behind a recurrence.  y [T, width] floats, gate rows of some wider matrix
 // (gate[t * gate_stride + i]), weight [width] floats; the row is cut into `parts` equal parts,
@@ -473,6 +550,17 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
   a.segment_state = segment_state; a.segment_decay = segment_decay;
   a.num_slots = num_slots; a.heads = heads; a.groups = groups; a.dim = dim; a.vdim = vdim; a.act = act;
   a.segments = segments; a.segment_len = segment_len;
+  // A step of single tokens (segment_len 1 says so): the streaming kernel, where it takes the sizes.
+  if (segments == 1 && segment_len == 1 && vdim % 4 == 0 && kRecurrenceThreads % (vdim / 4) == 0 &&
+      state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
+    a.lanes_per_column = 0; a.dim_pad = dim; a.batch = 1;
+    const int row_groups = kRecurrenceThreads / (vdim / 4);
+    const size_t bytes = (size_t)(2 * dim + vdim + row_groups * vdim) * sizeof(float);
+    const dim3 step_grid(heads, num_requests);
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(recurrence_step_kernel<T>, step_grid, kRecurrenceThreads, bytes, stream, a);
+    })
+  }
   int lanes = 1;
   while (lanes * rows < dim) lanes <<= 1;
   a.lanes_per_column = lanes;

@@ -203,7 +203,7 @@ def test_linear_recurrence_keeps_its_state(dev, dtype, heads, groups, dim, vdim,
     slots = torch.tensor([1, -1, 3, 0], dtype=torch.int32, device=dev)
     base = torch.randn((4, 5 + heads * dim * vdim), generator=gen).to(dev)
     state_got, state_want = base.clone(), base.clone()
-    for lengths in ((1, 3, 17, 0), (40, 1, 1, 2)):
+    for lengths in ((1, 3, 17, 0), (40, 1, 1, 2), (1, 1, 1, 1)):     # the last: a step of single tokens
         q_start, _ = _packed(lengths, dev)
         tokens = sum(lengths)
         wide = (torch.randn((tokens, 8 + 2 * groups * dim + heads * vdim), generator=gen) * 0.5).to(dtype).to(dev)
