@@ -116,19 +116,7 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long in_
 // Portions of up to segment_len tokens (decoding among them) take the emitting pass alone, which
 // then reads and writes the slot itself.
 // ---------------------------------------------------------------------------
-// Shared memory by its own instructions: the staged inputs are read once per token by every thread.
-// (volatile keeps them in order among themselves and with the barriers; no memory clobber, so that
-// the arithmetic of one token may be scheduled around the loads of the next.)
-__device__ __forceinline__ float4 lds128(uint32_t address) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address));
-  return v;
-}
-__device__ __forceinline__ float lds32(uint32_t address) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
-  return v;
-}
+// Stores into the staging buffers by the shared-memory instruction itself.
 __device__ __forceinline__ void sts32(uint32_t address, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
 }
@@ -286,13 +274,13 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
   float* y_out = a.y + ((long long)first * a.heads + head) * a.vdim + col;
   const long long y_step = (long long)a.heads * a.vdim;
   for (int t0 = first; t0 < last; t0 += batch, turn ^= 1) {
-    const uint32_t buffer = smem_base + 4u * (turn * buffer_floats);
     const bool more = t0 + batch < last;
     if (more) fetch(t0 + batch);   // on its way while this batch is added
-    const uint32_t kb = buffer + 4u * r0;
-    const uint32_t qb = kb + 4u * kq_floats;
-    const uint32_t vb = buffer + 4u * (v_offset + local_column);
-    const uint32_t ab = buffer + 4u * a_offset;
+    const float* bf = smem + turn * buffer_floats;
+    const float* kb = bf + r0;
+    const float* qb = kb + kq_floats;
+    const float* vb = bf + v_offset + local_column;
+    const float* ab = bf + a_offset;
     const int n = min(batch, last - t0);
     // kTokens tokens in a row: the state is updated token after token, the lanes' parts of the kTokens
     // outputs are added across the lanes together (shuffles of different tokens overlap).
@@ -301,13 +289,15 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
       float yp[kTokens], vcs[kTokens];
 #pragma unroll
       for (int u = 0; u < kTokens; ++u) {
-        const float ac = lds32(ab + 4u * (tt + u)), vc = lds32(vb + 4u * ((tt + u) * columns_per_block));
-        const float sv = lds32(ab + 4u * (batch + tt + u)) * vc;
+        const float ac = ab[tt + u], vc = vb[(tt + u) * columns_per_block];
+        const float sv = ab[batch + tt + u] * vc;
+        const float4* k4 = reinterpret_cast<const float4*>(kb + (tt + u) * dim_pad);
+        const float4* q4 = reinterpret_cast<const float4*>(qb + (tt + u) * dim_pad);
         float4 kc[ROWS / 4], qc[ROWS / 4];
 #pragma unroll
         for (int i = 0; i < ROWS / 4; ++i) {
-          kc[i] = lds128(kb + 4u * ((tt + u) * dim_pad + 4 * i));
-          if (kEmit) qc[i] = lds128(qb + 4u * ((tt + u) * dim_pad + 4 * i));
+          kc[i] = k4[i];
+          if (kEmit) qc[i] = q4[i];
         }
         float y4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -365,14 +355,24 @@ __global__ void recurrence_walk_kernel(const __grid_constant__ RecurrenceArgs a)
   const int slot = a.state_slots[r];
   const long long per_head = (long long)a.dim * a.vdim;
   float* slot_state = (slot >= 0 && slot < a.num_slots) ? a.state + (long long)slot * a.state_stride + head * per_head : nullptr;
+  constexpr int kAtOnce = 16;      // segments whose B and P are in registers before the chain of products starts
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < per_head; e += (long long)gridDim.x * blockDim.x) {
     float current = slot_state ? slot_state[e] : 0.f;
-    for (int segment = 0; segment < num_segments; ++segment) {
-      const long long index = (long long)r * a.segments + segment;
-      float* at = a.segment_state + (index * a.heads + head) * per_head + e;
-      const float b = *at;
-      *at = current;
-      current = fmaf(a.segment_decay[index * a.heads + head], current, b);
+    for (int base = 0; base < num_segments; base += kAtOnce) {
+      float b[kAtOnce], p[kAtOnce];
+#pragma unroll
+      for (int u = 0; u < kAtOnce; ++u) {
+        const long long index = (long long)r * a.segments + min(base + u, num_segments - 1);
+        b[u] = a.segment_state[(index * a.heads + head) * per_head + e];
+        p[u] = a.segment_decay[index * a.heads + head];
+      }
+#pragma unroll
+      for (int u = 0; u < kAtOnce; ++u) {
+        if (base + u >= num_segments) break;
+        const long long index = (long long)r * a.segments + base + u;
+        a.segment_state[(index * a.heads + head) * per_head + e] = current;
+        current = fmaf(p[u], current, b[u]);
+      }
     }
     if (slot_state) slot_state[e] = current;
   }
