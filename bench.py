@@ -653,10 +653,14 @@ def tepavik_kernels(peak: dict) -> dict:
                 rate(key, _graph_time_us(scan, copies), nbytes=moved, flops=4 * tokens * state_floats)
                 out[key + "_plan"] = list(ops.recurrence_plan(requests, max(lengths), r_heads, dim, vdim))
                 if tokens > requests:     # a prompt: the same in one segment, and with every number of rows per thread
-                    for rows in (4, 8, 16):
-                        out[f"{key}_one_segment_rows{rows}_us"] = round(_graph_time_us(
-                            lambda: scan(rows=rows, segment_len=tokens), copies), 1)
-                        out[f"{key}_segments_rows{rows}_us"] = round(_graph_time_us(lambda: scan(rows=rows), copies), 1)
+                    for rows, columns in ((4, 1), (8, 1), (16, 1), (16, 2)):
+                        name = f"rows{rows}" + ("x2" if columns == 2 else "")
+                        out[f"{key}_one_segment_{name}_us"] = round(_graph_time_us(
+                            lambda: scan(rows=rows, columns=columns, segment_len=tokens), copies), 1)
+                        out[f"{key}_segments_{name}_us"] = round(_graph_time_us(
+                            lambda: scan(rows=rows, columns=columns), copies), 1)
+                    out[f"{key}_segments64_rows16x2_us"] = round(_graph_time_us(
+                        lambda: scan(rows=16, columns=2, segment_len=64), copies), 1)
     out["status"] = int(status)
     return out
 

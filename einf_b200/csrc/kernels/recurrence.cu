@@ -139,15 +139,18 @@ struct RecurrenceArgs {
 };
 
 // kEmit false: the first pass (no queries, no output, state from zero into segment_state).
-template <typename T, int ROWS, bool kEmit>
-__global__ void __launch_bounds__(kRecurrenceThreads, 4)
+// COLS columns of the state per thread (COLS * ROWS registers of S): with two, the k and q a thread
+// reads from shared memory for a token serve twice as many state elements.
+template <typename T, int ROWS, int COLS, bool kEmit>
+__global__ void __launch_bounds__(kRecurrenceThreads, COLS == 1 ? 4 : 3)
 linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int lanes = a.lanes_per_column;          // a power of two, 1 .. 32
   const int columns_per_warp = 32 / lanes;
-  const int columns_per_block = (kRecurrenceThreads / 32) * columns_per_warp;
+  const int thread_columns = (kRecurrenceThreads / 32) * columns_per_warp;   // columns side by side over the threads
+  const int columns_per_block = COLS * thread_columns;                        // thread c-th column: + c * thread_columns
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / columns_per_warp;       // which rows of the column
   const int local_column = warp * columns_per_warp + (lane % columns_per_warp);
@@ -162,8 +165,13 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
   const int first = request_first + segment * a.segment_len;
   const int last = min(request_last, first + a.segment_len);
   const int slot = a.state_slots[r];
-  const bool live = column0 + local_column < a.vdim;
-  const int col = live ? column0 + local_column : a.vdim - 1;     // idle lanes follow along and write nothing
+  bool live[COLS];
+  int col[COLS];
+#pragma unroll
+  for (int c = 0; c < COLS; ++c) {
+    live[c] = column0 + c * thread_columns + local_column < a.vdim;
+    col[c] = live[c] ? column0 + c * thread_columns + local_column : a.vdim - 1;   // idle lanes follow along and write nothing
+  }
   const int r0 = part * ROWS;
   const int dim = a.dim, dim_pad = a.dim_pad, batch = a.batch;
 
@@ -174,7 +182,7 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
 
   const float* start_state = nullptr;
   float* end_state = nullptr;
-  const long long in_head = ((long long)head * dim) * a.vdim + col;
+  const long long in_head = ((long long)head * dim) * a.vdim;
   if (kEmit) {
     if (num_segments == 1) {
       if (slot >= 0 && slot < a.num_slots) start_state = a.state + (long long)slot * a.state_stride + in_head;
@@ -187,9 +195,12 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
   } else {
     end_state = a.segment_state + ((long long)blockIdx.z * a.heads * dim) * a.vdim + in_head;
   }
-  float S[ROWS];
+  float S[COLS][ROWS];
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) S[i] = (start_state && r0 + i < dim) ? start_state[(long long)(r0 + i) * a.vdim] : 0.f;
+  for (int c = 0; c < COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+      S[c][i] = (start_state && r0 + i < dim) ? start_state[(long long)(r0 + i) * a.vdim + col[c]] : 0.f;
 
   const T* qg = (const T*)a.q + (long long)group * dim;
   const T* kg = (const T*)a.k + (long long)group * dim;
@@ -271,7 +282,7 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
   __syncthreads();
   float decay_product = 1.f;
   int turn = 0;
-  float* y_out = a.y + ((long long)first * a.heads + head) * a.vdim + col;
+  float* y_out = a.y + ((long long)first * a.heads + head) * a.vdim;
   const long long y_step = (long long)a.heads * a.vdim;
   for (int t0 = first; t0 < last; t0 += batch, turn ^= 1) {
     const bool more = t0 + batch < last;
@@ -286,11 +297,10 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
     // outputs are added across the lanes together (shuffles of different tokens overlap).
     auto tokens = [&](int tt, auto count_tag) {
       constexpr int kTokens = decltype(count_tag)::value;
-      float yp[kTokens], vcs[kTokens];
+      float yp[COLS][kTokens], vcs[COLS][kTokens];
 #pragma unroll
       for (int u = 0; u < kTokens; ++u) {
-        const float ac = ab[tt + u], vc = vb[(tt + u) * columns_per_block];
-        const float sv = ab[batch + tt + u] * vc;
+        const float ac = ab[tt + u], scale = ab[batch + tt + u];
         const float4* k4 = reinterpret_cast<const float4*>(kb + (tt + u) * dim_pad);
         const float4* q4 = reinterpret_cast<const float4*>(qb + (tt + u) * dim_pad);
         float4 kc[ROWS / 4], qc[ROWS / 4];
@@ -299,32 +309,43 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
           kc[i] = k4[i];
           if (kEmit) qc[i] = q4[i];
         }
-        float y4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < ROWS / 4; ++i) {
-          S[4 * i + 0] = fmaf(ac, S[4 * i + 0], kc[i].x * sv);
-          S[4 * i + 1] = fmaf(ac, S[4 * i + 1], kc[i].y * sv);
-          S[4 * i + 2] = fmaf(ac, S[4 * i + 2], kc[i].z * sv);
-          S[4 * i + 3] = fmaf(ac, S[4 * i + 3], kc[i].w * sv);
-          if (kEmit) {
-            y4[0] = fmaf(S[4 * i + 0], qc[i].x, y4[0]);
-            y4[1] = fmaf(S[4 * i + 1], qc[i].y, y4[1]);
-            y4[2] = fmaf(S[4 * i + 2], qc[i].z, y4[2]);
-            y4[3] = fmaf(S[4 * i + 3], qc[i].w, y4[3]);
+        for (int c = 0; c < COLS; ++c) {
+          const float vc = vb[(tt + u) * columns_per_block + c * thread_columns];
+          const float sv = scale * vc;
+          float y4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < ROWS / 4; ++i) {
+            S[c][4 * i + 0] = fmaf(ac, S[c][4 * i + 0], kc[i].x * sv);
+            S[c][4 * i + 1] = fmaf(ac, S[c][4 * i + 1], kc[i].y * sv);
+            S[c][4 * i + 2] = fmaf(ac, S[c][4 * i + 2], kc[i].z * sv);
+            S[c][4 * i + 3] = fmaf(ac, S[c][4 * i + 3], kc[i].w * sv);
+            if (kEmit) {
+              y4[0] = fmaf(S[c][4 * i + 0], qc[i].x, y4[0]);
+              y4[1] = fmaf(S[c][4 * i + 1], qc[i].y, y4[1]);
+              y4[2] = fmaf(S[c][4 * i + 2], qc[i].z, y4[2]);
+              y4[3] = fmaf(S[c][4 * i + 3], qc[i].w, y4[3]);
+            }
           }
+          yp[c][u] = (y4[0] + y4[1]) + (y4[2] + y4[3]);
+          vcs[c][u] = vc;
         }
-        yp[u] = (y4[0] + y4[1]) + (y4[2] + y4[3]);
-        vcs[u] = vc;
         if (!kEmit) decay_product *= ac;
       }
       if (kEmit) {
         for (int o = columns_per_warp; o < 32; o <<= 1) {
 #pragma unroll
-          for (int u = 0; u < kTokens; ++u) yp[u] += __shfl_xor_sync(0xffffffffu, yp[u], o);
-        }
-        if (live && part == 0) {
+          for (int c = 0; c < COLS; ++c)
 #pragma unroll
-          for (int u = 0; u < kTokens; ++u) y_out[u * y_step] = yp[u] + skip * vcs[u];
+            for (int u = 0; u < kTokens; ++u) yp[c][u] += __shfl_xor_sync(0xffffffffu, yp[c][u], o);
+        }
+        if (part == 0) {
+#pragma unroll
+          for (int c = 0; c < COLS; ++c)
+            if (live[c]) {
+#pragma unroll
+              for (int u = 0; u < kTokens; ++u) y_out[u * y_step + col[c]] = yp[c][u] + skip * vcs[c][u];
+            }
         }
         y_out += kTokens * y_step;
       }
@@ -335,10 +356,14 @@ linear_recurrence_kernel(const __grid_constant__ RecurrenceArgs a) {
     if (more) stash(smem_base + 4u * ((turn ^ 1) * buffer_floats));
     __syncthreads();
   }
-  if (end_state && live) {
+  if (end_state) {
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i)
-      if (r0 + i < dim) end_state[(long long)(r0 + i) * a.vdim] = S[i];
+    for (int c = 0; c < COLS; ++c)
+      if (live[c]) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i)
+          if (r0 + i < dim) end_state[(long long)(r0 + i) * a.vdim + col[c]] = S[c][i];
+      }
   }
   if (!kEmit && blockIdx.x == 0 && threadIdx.x == 0) a.segment_decay[(long long)blockIdx.z * a.heads + head] = decay_product;
 }
@@ -521,15 +546,17 @@ extern "C" int einf_conv_silu(const void* in, int dtype, long long in_stride, co
   })
 }
 
-// rows per thread: 0 lets the launcher choose among 16, 8 and 4.  segments > 1 needs segment_state [requests * segments,
+// rows per thread: 0 lets the launcher choose among 16, 8 and 4; columns per thread: 0 (the launcher's
+// choice), 1, or 2 (with 16 rows).  segments > 1 needs segment_state [requests * segments,
 // heads, dim, vdim] and segment_decay [requests * segments, heads].
 extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* v, int dtype, long long q_stride,
                                       long long k_stride, long long v_stride, const float* head_decay,
                                       const float* token_decay, const float* token_scale, const float* skip,
                                       float* state, long long state_stride, int num_slots, const int* q_start,
                                       const int* state_slots, int num_requests, float* y, int heads, int groups,
-                                      int dim, int vdim, int act, int rows, int segments, int segment_len,
-                                      float* segment_state, float* segment_decay, cudaStream_t stream) {
+                                      int dim, int vdim, int act, int rows, int columns, int segments,
+                                      int segment_len, float* segment_state, float* segment_decay,
+                                      cudaStream_t stream) {
   if (num_requests == 0) return 0;
   if (heads <= 0 || groups <= 0 || heads % groups || dim <= 0 || vdim <= 0 || dim > 512 || heads > 65535 ||
       segments < 1 || segment_len < 1 || (long long)num_requests * segments > 65535 ||
@@ -565,7 +592,15 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
   while (lanes * rows < dim) lanes <<= 1;
   a.lanes_per_column = lanes;
   a.dim_pad = lanes * rows;
-  const int columns_per_block = (kRecurrenceThreads / 32) * (32 / lanes);
+  // Two columns a thread where the state is wide enough for it and the launch still has CTAs for
+  // the whole GPU (or the caller says so).
+  const int thread_columns = (kRecurrenceThreads / 32) * (32 / lanes);
+  if (columns == 0) {
+    const long long ctas = (long long)((vdim + 2 * thread_columns - 1) / (2 * thread_columns)) * heads * num_requests * segments;
+    columns = (rows == 16 && vdim >= 2 * thread_columns && ctas >= 2 * 148) ? 2 : 1;
+  }
+  if (columns != 1 && !(columns == 2 && rows == 16)) return (int)cudaErrorInvalidValue;
+  const int columns_per_block = columns * thread_columns;
   int batch = kStageKQ * kRecurrenceThreads / dim;
   if (batch > kStageV * kRecurrenceThreads / columns_per_block) batch = kStageV * kRecurrenceThreads / columns_per_block;
   if (batch > kMaxBatch) batch = kMaxBatch;
@@ -576,10 +611,10 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
     const int floats = ((emit ? 2 : 1) * batch * a.dim_pad + batch * columns_per_block + 2 * batch + 3) & ~3;
     return (size_t)2 * floats * sizeof(float);
   };
-#define EINF_RECURRENCE_ROWS(ROWS_)                                                                                   \
+#define EINF_RECURRENCE_ROWS(ROWS_, COLS_)                                                                                   \
   {                                                                                                                   \
     if (segments > 1) {                                                                                               \
-      cudaError_t e = launch_pdl(linear_recurrence_kernel<T, ROWS_, false>, grid, kRecurrenceThreads,                 \
+      cudaError_t e = launch_pdl(linear_recurrence_kernel<T, ROWS_, COLS_, false>, grid, kRecurrenceThreads,          \
                                  buffer_bytes(false), stream, a);                                                     \
       if (e != cudaSuccess) return (int)e;                                                                            \
       const long long per_head = (long long)dim * vdim;                                                               \
@@ -587,13 +622,14 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
       e = launch_pdl(recurrence_walk_kernel, walk_grid, 256, 0, stream, a);                                           \
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
-    return (int)launch_pdl(linear_recurrence_kernel<T, ROWS_, true>, grid, kRecurrenceThreads, buffer_bytes(true),   \
+    return (int)launch_pdl(linear_recurrence_kernel<T, ROWS_, COLS_, true>, grid, kRecurrenceThreads, buffer_bytes(true), \
                            stream, a);                                                                                \
   }
   EINF_DISPATCH_2(dtype, T, {
-    if (rows == 16) EINF_RECURRENCE_ROWS(16)
-    if (rows == 8) EINF_RECURRENCE_ROWS(8)
-    EINF_RECURRENCE_ROWS(4)
+    if (rows == 16 && columns == 2) EINF_RECURRENCE_ROWS(16, 2)
+    if (rows == 16) EINF_RECURRENCE_ROWS(16, 1)
+    if (rows == 8) EINF_RECURRENCE_ROWS(8, 1)
+    EINF_RECURRENCE_ROWS(4, 1)
   })
 #undef EINF_RECURRENCE_ROWS
 }

@@ -744,6 +744,7 @@ def linear_recurrence(
     max_q_len: Optional[int] = None,
     rows: int = 0,
     segment_len: Optional[int] = None,
+    columns: int = 0,
 ) -> None:
     """Per request and head, over its tokens in order, with a float32 state ``S [dim, vdim]``::
 
@@ -756,8 +757,8 @@ def linear_recurrence(
     they are read.  ``state [slots, heads, dim, vdim]`` float32 (slot stride may be larger) is read
     at the start of each request's portion and written at its end; ``y [tokens, heads * vdim]``
     float32.  ``max_q_len`` is the longest portion of the step as the host knows it (None: unknown,
-    no portion is cut into segments); ``rows`` (0, 4, 8, 16) and ``segment_len`` override the
-    launch's own choices (:func:`recurrence_plan`), for tests and measurements."""
+    no portion is cut into segments); ``rows`` (0, 4, 8, 16), ``columns`` (0, 1, 2) and ``segment_len``
+    override the launch's own choices (:func:`recurrence_plan`), for tests and measurements."""
     tokens = v.shape[0]
     if q.shape != (tokens, groups * dim) or k.shape != q.shape or v.shape != (tokens, heads * vdim):
         raise ValueError(f"q, k must be [{tokens}, {groups * dim}] and v [{tokens}, {heads * vdim}]")
@@ -796,7 +797,7 @@ def linear_recurrence(
         "einf_linear_recurrence",
         [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-         c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     )
     _check(
         fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), _code(q), _rows_of(q, "q"), _rows_of(k, "k"), _rows_of(v, "v"),
@@ -804,7 +805,7 @@ def linear_recurrence(
            _opt(token_scale, "token_scale", torch.float32), _opt(skip, "skip", torch.float32),
            state.data_ptr(), state.stride(0), state.shape[0], _opt(q_start, "q_start", torch.int32),
            _opt(state_slots, "state_slots", torch.int32), requests, _dev(y, "y"), heads, groups, dim,
-           vdim, 1 if silu_inputs else 0, int(rows), segments, segment_len,
+           vdim, 1 if silu_inputs else 0, int(rows), int(columns), segments, segment_len,
            _opt(segment_state, "segment_state", torch.float32), _opt(segment_decay, "segment_decay", torch.float32),
            _stream()),
         "linear_recurrence",

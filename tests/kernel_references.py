@@ -188,7 +188,7 @@ def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, o
 
 def linear_recurrence(q, k, v, state, q_start, state_slots, y, heads, groups, dim, vdim, head_decay=None,
                       token_decay=None, token_scale=None, skip=None, silu_inputs=False, max_q_len=None, rows=0,
-                      segment_len=None):
+                      segment_len=None, columns=0):
     def act(t):
         t = t.float()
         return t / (1 + torch.exp(-t)) if silu_inputs else t

@@ -190,8 +190,10 @@ def test_conv_silu_carries_its_inputs(dev, dtype, channels, taps, heads):
     (3, 3, 24, 16, False, True), (4, 2, 8, 12, True, False), (2, 1, 128, 64, True, False), (1, 1, 40, 8, False, True),
     (6, 3, 20, 8, True, False), (2, 2, 16, 130, False, False), (8, 8, 64, 64, False, True), (2, 1, 300, 20, True, False),
 ])
-@pytest.mark.parametrize("rows, segment_len", [(0, None), (4, 3), (8, None), (16, 16), (0, 5)])
-def test_linear_recurrence_keeps_its_state(dev, dtype, heads, groups, dim, vdim, per_token, silu, rows, segment_len):
+@pytest.mark.parametrize("rows, segment_len, columns", [(0, None, 0), (4, 3, 1), (8, None, 1), (16, 16, 2), (0, 5, 0),
+                                                        (16, None, 2)])
+def test_linear_recurrence_keeps_its_state(dev, dtype, heads, groups, dim, vdim, per_token, silu, rows, segment_len,
+                                           columns):
     """Two steps on the same slots (one request without a slot), portions of one token and of many,
     an empty request; inputs as columns of a wider matrix; every number of rows per thread; portions
     cut into segments that run side by side; outputs and states against the plain loop."""
@@ -220,7 +222,7 @@ def test_linear_recurrence_keeps_its_state(dev, dtype, heads, groups, dim, vdim,
         for fn, state in ((ops.linear_recurrence, state_got), (ref.linear_recurrence, state_want)):
             y = torch.zeros((tokens, heads * vdim), device=dev)
             fn(q, k, v, state[:, 5:].view(4, heads, dim, vdim), q_start, slots, y, heads, groups, dim, vdim,
-               max_q_len=max(lengths), rows=rows, segment_len=segment_len, **kwargs)
+               max_q_len=max(lengths), rows=rows, segment_len=segment_len, columns=columns, **kwargs)
             ys.append(y)
         torch.testing.assert_close(ys[0], ys[1], rtol=2e-4, atol=2e-4)
         torch.testing.assert_close(state_got, state_want, rtol=2e-4, atol=2e-4)
