@@ -708,14 +708,27 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
           auto exps = [&](float* sv, int c0, bool masked_already) {
             if (kMasked && !masked_already) mask(sv, c0);
             if (has_cap) {
-              // a masked score is -inf: 2^-inf = 0, the reciprocal of 1 is 1, the capped score -cap; it
-              // has to stay -inf
-#pragma unroll
-              for (int c = 0; c < 32; ++c) sv[c] = sv[c] == -INFINITY ? -INFINITY : capped(sv[c], sc) - m_use;
+              // cap * tanh(x) - m as -2 cap / (2^(2 x log2 e) + 1) + (cap - m), two scores to an
+              // instruction where there is one that takes two.  A masked score is -inf: 2^-inf = 0,
+              // the reciprocal of 1 is 1, the capped score -cap; it has to stay -inf (only the walk
+              // with masks meets one).
+              const float2 in2 = make_float2(sc.tanh_in, sc.tanh_in), zero2 = make_float2(0.f, 0.f);
+              const float2 one2 = make_float2(1.f, 1.f), down2 = make_float2(-2.f * sc.cap_log2, -2.f * sc.cap_log2);
+              const float2 off2 = make_float2(sc.cap_log2 - m_use, sc.cap_log2 - m_use);
 #pragma unroll
               for (int c = 0; c < 32; c += 2) {
-                sv[c] = fast_exp2(sv[c]);
-                sv[c + 1] = fast_exp2(sv[c + 1]);
+                const float2 x = __ffma2_rn(make_float2(sv[c], sv[c + 1]), in2, zero2);
+                const float2 e = __fadd2_rn(make_float2(fast_exp2(x.x), fast_exp2(x.y)), one2);
+                float2 inv;
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv.x) : "f"(e.x));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv.y) : "f"(e.y));
+                float2 z = __ffma2_rn(inv, down2, off2);
+                if (kMasked) {
+                  z.x = sv[c] == -INFINITY ? -INFINITY : z.x;
+                  z.y = sv[c + 1] == -INFINITY ? -INFINITY : z.y;
+                }
+                sv[c] = fast_exp2(z.x);
+                sv[c + 1] = fast_exp2(z.y);
                 sum2 = __fadd2_rn(sum2, make_float2(sv[c], sv[c + 1]));
               }
               return;
