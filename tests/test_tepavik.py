@@ -204,6 +204,20 @@ def test_random_weights_mode_writes_a_folder_the_loader_takes(tmp_path):
     assert float(tensors["l0.norm1"].float().abs().max()) < 0.5      # stored around zero
 
 
+def test_long_portions_are_cut_into_segments_only_where_that_fills_the_gpu():
+    from einf_b200 import ops
+
+    plan = ops.recurrence_plan
+    assert plan(8, 1, 14, 64, 64, sms=148) == (1, 1)                 # decoding: the streaming kernel
+    assert plan(4, 100, 14, 64, 64, sms=148) == (1, 100)             # short portions: one pass
+    assert plan(1, 2048, 14, 64, 64, sms=148) == (16, 128)           # one prompt: sixteen segments
+    assert plan(64, 2048, 32, 128, 128, sms=148) == (1, 2048)        # requests and heads fill the GPU already
+    segments, length = plan(1, 100_000, 14, 64, 64, sms=148)         # at most 64 segments, whole tokens in all
+    assert segments <= ops.MAX_SEGMENTS and segments * length >= 100_000 and length % 16 == 0
+    segments, length = plan(4000, 300, 2, 16, 16, sms=148)           # requests x segments stay within the grid
+    assert 4000 * segments <= 65535 and segments * length >= 300
+
+
 # ---------------------------------------------------------------------------
 # the engine on the plain statements of the kernels (CPU)
 @pytest.fixture()
