@@ -41,7 +41,14 @@ class CacheStorage:
         self.views: list[CacheView] = []
         for index, entry in enumerate(plan.entries):
             need = entry.need
-            if entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size != need.head_size:
+            if entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size == 0:
+                # the values are read out of the key rows: keys only
+                pages = self.pages_per_group[entry.group]
+                self._owned[index] = (
+                    torch.zeros((pages, need.num_kv_heads, page_size, need.head_size), dtype=dtype, device=device),
+                    None,
+                )
+            elif entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size != need.head_size:
                 # keys and values of different sizes: one tensor each
                 pages = self.pages_per_group[entry.group]
                 self._owned[index] = tuple(
@@ -78,5 +85,7 @@ class CacheStorage:
         total = 0
         for owned in self._owned.values():
             for t in (owned if isinstance(owned, tuple) else (owned,)):
+                if t is None:
+                    continue
                 total += t.numel() * t.element_size()
         return total

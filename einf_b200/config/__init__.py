@@ -1,5 +1,6 @@
 """Typed configurations and the architecture registry."""
 from .base import ConfigError, ModelConfig
+from .bomipel import BomipelConfig
 from .engine import EngineConfig
 from .qwen2 import Qwen2Config
 from .registry import (
@@ -14,8 +15,10 @@ from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
 
 register_architecture(Qwen2Config)
 register_architecture(TepavikConfig)
+register_architecture(BomipelConfig)
 
 __all__ = [
+    "BomipelConfig",
     "ConfigError",
     "EngineConfig",
     "LayerSpec",

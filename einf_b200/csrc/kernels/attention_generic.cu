@@ -16,12 +16,17 @@
 // chunk size c (chunked attention) lo is also at least floor(p / c) * c, the first position of p's
 // own chunk, counted from position 0 of the sequence.  With a soft cap z the scaled score s becomes
 // z * tanh(s / z) before the softmax.  Keys and values may have different sizes per head.
+// With `keep_first` n > 0 a windowed token also sees the first n positions of its sequence
+// (j < n), at their true positions.  `value_stride` is the distance between two value rows in
+// elements: value_size for a cache of its own, the key size when the values are the leading
+// elements of the key rows (a latent cache that holds one row per token for both).
+// The kernel exists twice: for sizes up to 256 and for sizes up to 640 (more registers a lane).
 #include "common.cuh"
 
 namespace einf {
 
 constexpr int kWarpsPerBlock = 4;
-constexpr int kMaxHeadSize = 256;
+constexpr int kMaxHeadSize = 640;
 
 template <typename T>
 struct Vec;  // 16-byte vector of T
@@ -41,15 +46,16 @@ struct Vec<__nv_bfloat16> {
   }
 };
 
-template <typename T>
+template <typename T, int kHeadLimit>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                                const T* __restrict__ v_cache, const int* __restrict__ block_table,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                T* __restrict__ out, int num_rows, int num_heads, int num_kv_heads,
-                               int head_size, int value_size, int page_size, int num_pages, int table_width,
-                               float scale, int window, int chunk, float softcap, int* status) {
-  __shared__ float q_smem[kWarpsPerBlock][kMaxHeadSize];
+                               int head_size, int value_size, int value_stride, int page_size, int num_pages,
+                               int table_width, float scale, int window, int keep_first, int chunk, float softcap,
+                               int* status) {
+  __shared__ float q_smem[kWarpsPerBlock][kHeadLimit];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -71,18 +77,24 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   __syncwarp();
   const float* qs = q_smem[warp];
 
-  constexpr int kDimsPerLane = kMaxHeadSize / 32;
+  constexpr int kDimsPerLane = kHeadLimit / 32;
   float acc[kDimsPerLane];
 #pragma unroll
   for (int i = 0; i < kDimsPerLane; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
   bool bad_page = false;
 
-  for (int base = lo; base <= pos; base += 32) {
+  // Two ranges of keys: the kept first positions below the window (empty without them), then
+  // the window itself.
+  const int kept = (window > 0 && keep_first > 0) ? min(keep_first, lo) : 0;
+  for (int range = kept > 0 ? 0 : 1; range < 2; ++range) {
+  const int first = range == 0 ? 0 : lo;
+  const int last = range == 0 ? kept - 1 : pos;
+  for (int base = first; base <= last; base += 32) {
     const int j = base + lane;
     float s = -INFINITY;
     long long key_row = -1;  // index of the (page, kv_head, slot) row in the caches, or -1
-    if (j <= pos) {
+    if (j <= last) {
       const int logical = j / page_size;
       const int page = table[logical];
       if (page < 0 || page >= num_pages) {
@@ -105,25 +117,27 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
-    // m_new is finite: key `pos` itself is always visible unless its page is bad.
+    // m_new is finite unless every key so far had a bad page (the kept range comes first, so
+    // key `pos` itself may still be ahead): then nothing is added.
     const float p = (s == -INFINITY) ? 0.f : expf(s - m_new);
     const float correction = (m == -INFINITY) ? 0.f : expf(m - m_new);
     l = l * correction + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < kDimsPerLane; ++i) acc[i] *= correction;
     m = m_new;
-    const int count = min(32, pos - base + 1);
+    const int count = min(32, last - base + 1);
     for (int kk = 0; kk < count; ++kk) {
       const float pj = __shfl_sync(0xffffffffu, p, kk);
       const long long off = __shfl_sync(0xffffffffu, key_row, kk);
       if (off < 0) continue;
-      const T* v_row = v_cache + off * value_size;
+      const T* v_row = v_cache + off * value_stride;
 #pragma unroll
       for (int i = 0; i < kDimsPerLane; ++i) {
         const int d = lane + 32 * i;
         if (d < value_size) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
       }
     }
+  }
   }
   if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(status, kStatusBadPage);
   const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -143,19 +157,27 @@ extern "C" int einf_paged_attention_generic(const void* q, const void* k_cache, 
                                             int dtype, const int* block_table, const int* seq_of_token,
                                             const int* positions, void* out, int num_tokens,
                                             int num_heads, int num_kv_heads, int head_size, int value_size,
-                                            int page_size, int num_pages, int table_width, float scale,
-                                            int window, int chunk, float softcap, int* status,
-                                            cudaStream_t stream) {
+                                            int value_stride, int page_size, int num_pages, int table_width,
+                                            float scale, int window, int keep_first, int chunk, float softcap,
+                                            int* status, cudaStream_t stream) {
   const int rows = num_tokens * num_heads;
   if (rows == 0) return 0;
   if (head_size > kMaxHeadSize || value_size > kMaxHeadSize || head_size <= 0 || value_size <= 0)
     return (int)cudaErrorInvalidValue;
   const int blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (value_stride < value_size) return (int)cudaErrorInvalidValue;
   EINF_DISPATCH_2(dtype, T, {
-    paged_attention_generic_kernel<T><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
-        (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
-        rows, num_heads, num_kv_heads, head_size, value_size, page_size, num_pages, table_width, scale, window,
-        chunk, softcap, status);
+    if (head_size <= 256 && value_size <= 256) {
+      paged_attention_generic_kernel<T, 256><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
+          (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
+          rows, num_heads, num_kv_heads, head_size, value_size, value_stride, page_size, num_pages, table_width,
+          scale, window, keep_first, chunk, softcap, status);
+    } else {
+      paged_attention_generic_kernel<T, kMaxHeadSize><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
+          (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
+          rows, num_heads, num_kv_heads, head_size, value_size, value_stride, page_size, num_pages, table_width,
+          scale, window, keep_first, chunk, softcap, status);
+    }
   })
   return (int)cudaGetLastError();
 }

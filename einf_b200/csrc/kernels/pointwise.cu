@@ -808,19 +808,31 @@ __global__ void activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __
 // x / sqrt(mean(x^2) + eps), in 32-bit, before it is rounded; values pass through.  Queries go to
 // q_out [T, H, key_size], keys and values into the pages at slots[t] (negative: not written):
 // k_cache [pages, G, page, key_size], v_cache [pages, G, page, value_size].
+// With `rotary_pairs` n > 0 the first 2n dimensions of every query and key head are rotated by
+// the token's position: pair i is (i, i + n) (`interleaved` 0) or (2i, 2i + 1) (`interleaved` 1),
+// (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * inv_freq[i], in 32-bit.
+// Value mixing across layers (`value_mix`): 1 = this layer is the source, its values are also
+// left in `shared_values` [T, G * value_size] (32-bit); 2 = its values become
+// (1 - m) v + m shared_values[t] with the scalar m = *mix, before they are cached.
 // ---------------------------------------------------------------------------
 template <typename TIn, typename T>
 __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
                                       const float* __restrict__ bias, const int* __restrict__ slots,
                                       T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                       int num_tokens, int num_heads, int num_kv_heads, int key_size, int value_size,
-                                      int normalise, float eps, int page_size, int num_pages, int* status) {
+                                      int normalise, float eps, int page_size, int num_pages,
+                                      const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                      int rotary_pairs, int interleaved, int value_mix,
+                                      float* __restrict__ shared_values, const void* __restrict__ mix, int mix_dtype,
+                                      int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int per_token = num_heads + 2 * num_kv_heads;
   if (warp >= (long long)num_tokens * per_token) return;
+  bool rotate = rotary_pairs > 0;
+  int value_head = -1;
   const int t = (int)(warp / per_token);
   const int item = (int)(warp - (long long)t * per_token);
   const int width = (num_heads + num_kv_heads) * key_size + num_kv_heads * value_size;
@@ -850,6 +862,8 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
       base = (num_heads + num_kv_heads) * key_size + head * value_size;
       dst = v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * value_size;
       unit = false;
+      rotate = false;
+      value_head = head;
     }
   }
   constexpr int kPerLane = 8;   // head sizes up to 256
@@ -868,6 +882,40 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
   }
   float factor = 1.f;
   if (unit) factor = rsqrtf(warp_sum(ss) / (float)size + eps);
+  if (rotate) {
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < 2 * rotary_pairs) {
+        // the other element of the pair comes from the product again (it lies in another lane)
+        int pair, other;
+        bool leads;
+        if (interleaved) {
+          pair = d >> 1; leads = (d & 1) == 0; other = d ^ 1;
+        } else {
+          leads = d < rotary_pairs; pair = leads ? d : d - rotary_pairs; other = leads ? d + rotary_pairs : pair;
+        }
+        float w = sum_splits(row + other, splits, split_stride);
+        if (bias) w += bias[base + other];
+        float sn, cs;
+        sincosf(pos * inv_freq[pair], &sn, &cs);
+        v[i] = leads ? v[i] * cs - w * sn : v[i] * cs + w * sn;
+      }
+    }
+  }
+  if (value_head >= 0 && value_mix) {
+    float* shared_row = shared_values + ((size_t)t * num_kv_heads + value_head) * value_size;
+    const float m = value_mix == 2 ? (mix_dtype == kFloat32 ? *(const float*)mix : to_float(*(const __nv_bfloat16*)mix)) : 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < size) {
+        if (value_mix == 1) shared_row[d] = v[i];
+        else v[i] = (1.f - m) * v[i] + m * shared_row[d];
+      }
+    }
+  }
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
     const int d = lane + 32 * i;
@@ -882,6 +930,15 @@ __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ b
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     out[idx] = from_float<T>(to_float(out[idx]) + bias[idx % n]);
   }
+}
+
+// out = cap * tanh(out / cap), in place: the soft cap on logits.
+__global__ void softcap_kernel(float* __restrict__ values, long long n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = 1.f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    values[i] = cap * tanhf(values[i] * inv);
 }
 
 }  // namespace einf
@@ -1158,9 +1215,14 @@ extern "C" int einf_activation(const void* x, int in_dtype, int splits, long lon
 extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, long long split_stride, int dtype,
                                    const float* bias, const int* slots, void* q_out, void* k_cache, void* v_cache,
                                    int num_tokens, int num_heads, int num_kv_heads, int key_size, int value_size,
-                                   int normalise, float eps, int page_size, int num_pages, int* status,
+                                   int normalise, float eps, int page_size, int num_pages, const int* positions,
+                                   const float* inv_freq, int rotary_pairs, int interleaved, int value_mix,
+                                   float* shared_values, const void* mix, int mix_dtype, int* status,
                                    cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  if (rotary_pairs < 0 || 2 * rotary_pairs > key_size || (rotary_pairs > 0 && (!positions || !inv_freq)))
+    return (int)cudaErrorInvalidValue;
+  if (value_mix && (!shared_values || (value_mix == 2 && !mix))) return (int)cudaErrorInvalidValue;
   if (key_size > 256 || value_size > 256 || key_size <= 0 || (num_kv_heads > 0 && value_size <= 0))
     return (int)cudaErrorInvalidValue;
   const long long warps = (long long)num_tokens * (num_heads + 2 * num_kv_heads);
@@ -1172,6 +1234,7 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
       return (int)launch_pdl(qkv_norm_store_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)qkv, splits,
                              (size_t)split_stride, bias, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_tokens,
                              num_heads, num_kv_heads, key_size, value_size, normalise, eps, page_size, num_pages,
+                             positions, inv_freq, rotary_pairs, interleaved, value_mix, shared_values, mix, mix_dtype,
                              status);
     })
   })
@@ -1188,4 +1251,12 @@ extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long 
     add_bias_kernel<T><<<(int)blocks, threads, 0, stream>>>((T*)out, bias, n, total);
   })
   return (int)cudaGetLastError();
+}
+
+extern "C" int einf_softcap(float* values, long long n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (int)launch_pdl(softcap_kernel, (int)blocks, 256, 0, stream, values, n, cap);
 }

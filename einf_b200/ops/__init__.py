@@ -27,6 +27,8 @@ STATUS_BAD_PAGE = 2
 STATUS_WAIT_EXPIRED = 4
 
 MAX_HEAD_SIZE = 256
+#: the general attention kernel alone takes larger heads (a latent cache row)
+MAX_GENERIC_HEAD_SIZE = 640
 
 
 class KernelError(RuntimeError):
@@ -495,7 +497,7 @@ def project(
 def paged_attention_generic(
     q: torch.Tensor,
     k_cache: torch.Tensor,
-    v_cache: torch.Tensor,
+    v_cache: Optional[torch.Tensor],
     block_table: torch.Tensor,
     seq_of_token: torch.Tensor,
     positions: torch.Tensor,
@@ -505,23 +507,35 @@ def paged_attention_generic(
     status: torch.Tensor,
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
+    keep_first: int = 0,
+    values_in_keys: Optional[int] = None,
 ) -> None:
     """Causal attention of every token of the batch over the pages of its request.
 
     ``q`` is ``[tokens, heads, head_size]``, ``out`` ``[tokens, heads, value_size]``; the caches
     ``[pages, kv_heads, page_size, head_size]`` and ``[pages, kv_heads, page_size, value_size]``;
     ``block_table`` ``[requests, width]`` maps a request's logical page to a physical one.
-    ``window``: only the last that many keys; ``chunk``: only the keys of the token's own block of
+    ``window``: only the last that many keys, and with ``keep_first`` n also the first n positions
+    of the sequence; ``chunk``: only the keys of the token's own block of
     that many positions (blocks counted from position 0); ``softcap`` z: scores become
-    ``z * tanh(score / z)`` before the softmax.
+    ``z * tanh(score / z)`` before the softmax.  ``values_in_keys`` n (with ``v_cache`` None): a
+    token's value is the first n elements of its key row (one cached row serves as both).
     """
     tokens, num_heads, head_size = q.shape
     num_pages, num_kv_heads, page_size, size = k_cache.shape
-    value_size = v_cache.shape[3]
-    if size != head_size or v_cache.shape[:3] != k_cache.shape[:3]:
+    if values_in_keys is not None:
+        if v_cache is not None or not 0 < values_in_keys <= size:
+            raise ValueError("values_in_keys takes no value cache and at most the key size")
+        v_cache, value_size, value_stride = k_cache, int(values_in_keys), size
+    else:
+        value_size = value_stride = v_cache.shape[3]
+        if v_cache.shape[:3] != k_cache.shape[:3]:
+            raise ValueError("key and value caches differ in pages, heads or page size")
+    if size != head_size:
         raise ValueError("cache head size differs from q")
-    if max(head_size, value_size) > MAX_HEAD_SIZE:
-        raise UnsupportedSize(f"paged attention takes head sizes up to {MAX_HEAD_SIZE}, got {head_size}, {value_size}")
+    if max(head_size, value_size) > MAX_GENERIC_HEAD_SIZE:
+        raise UnsupportedSize(
+            f"paged attention takes head sizes up to {MAX_GENERIC_HEAD_SIZE}, got {head_size}, {value_size}")
     if num_heads % num_kv_heads:
         raise UnsupportedSize(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
@@ -531,15 +545,15 @@ def paged_attention_generic(
     fn = _fn(
         "einf_paged_attention_generic",
         [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-         c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
            _opt(block_table, "block_table", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
            _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads,
-           head_size, value_size, page_size, num_pages, block_table.shape[1], float(scale),
-           int(window) if window else 0, int(chunk) if chunk else 0, float(softcap) if softcap else 0.0,
-           _dev(status, "status"), _stream()),
+           head_size, value_size, value_stride, page_size, num_pages, block_table.shape[1], float(scale),
+           int(window) if window else 0, int(keep_first) if window else 0, int(chunk) if chunk else 0,
+           float(softcap) if softcap else 0.0, _dev(status, "status"), _stream()),
         "paged_attention_generic",
     )
 
@@ -576,8 +590,19 @@ def qkv_norm_store(
     value_size: int,
     unit_eps: Optional[float],
     status: torch.Tensor,
+    positions: Optional[torch.Tensor] = None,
+    inv_freq: Optional[torch.Tensor] = None,
+    interleaved: bool = False,
+    value_mix: Optional[str] = None,
+    shared_values: Optional[torch.Tensor] = None,
+    mix: Optional[torch.Tensor] = None,
 ) -> None:
-    """For an attention layer without a rotation: add the bias, divide every query and key head by
+    """The general form of bias, position encoding and cache write.  With ``inv_freq`` (float32,
+    n entries; needs ``positions``) the first 2n dimensions of every query and key head are rotated
+    by ``position * inv_freq[i]``, pair i being dimensions (i, i + n), or (2i, 2i + 1) with
+    ``interleaved``.  ``value_mix`` "source" also leaves the layer's values in ``shared_values``
+    (float32 ``[tokens, kv_heads * value_size]``); "blend" caches ``(1 - m) v + m shared_values``
+    with the one-element float32 tensor ``mix``.  Without these: add the bias, divide every query and key head by
     its root mean square (``unit_eps`` inside the root; None: leave them), write the queries to
     ``q_out [tokens, heads, key_size]`` and keys and values into the pages at ``slots``.  A row of
     ``qkv`` (or of its float32 split-K partial sums) is ``[heads * key_size | kv_heads * key_size |
@@ -604,18 +629,243 @@ def qkv_norm_store(
         if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
             raise TypeError("cache dtype differs from q_out")
         k_ptr, v_ptr = _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
+    pairs = 0
+    if inv_freq is not None and inv_freq.shape[0]:
+        pairs = inv_freq.shape[0]
+        if positions is None or 2 * pairs > key_size:
+            raise ValueError("a rotation needs positions and at most key_size / 2 frequencies")
+    mix_code = {None: 0, "source": 1, "blend": 2}[value_mix]
+    if mix_code:
+        if shared_values is None or shared_values.dtype != torch.float32 or \
+                shared_values.numel() != tokens * num_kv_heads * value_size:
+            raise ValueError("value mixing needs float32 shared_values [tokens, kv_heads * value_size]")
+        if mix_code == 2 and (mix is None or mix.numel() != 1):
+            raise ValueError("value_mix 'blend' needs the one-element tensor mix")
     fn = _fn(
         "einf_qkv_norm_store",
         [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+         c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(qkv, "qkv"), _code(qkv), splits, stride, _code(q_out), _opt(bias, "bias", torch.float32),
            _opt(slots, "slots", torch.int32) if k_ptr else 0, _dev(q_out, "q_out"), k_ptr, v_ptr, tokens,
            num_heads, num_kv_heads, key_size, value_size, 0 if unit_eps is None else 1,
-           float(unit_eps or 0.0), page_size, num_pages, _dev(status, "status"), _stream()),
+           float(unit_eps or 0.0), page_size, num_pages,
+           _opt(positions, "positions", torch.int32) if pairs else 0,
+           _opt(inv_freq, "inv_freq", torch.float32) if pairs else 0, pairs, 1 if interleaved else 0, mix_code,
+           _opt(shared_values, "shared_values", torch.float32) if mix_code else 0,
+           _opt(mix, "mix", torch.float32) if mix_code == 2 else 0, FLOAT32, _dev(status, "status"), _stream()),
         "qkv_norm_store",
     )
+
+
+# ---------------------------------------------------------------------------
+# Latent attention
+def latent_down_store(
+    down: torch.Tensor,
+    q_rank: int,
+    kv_rank: int,
+    rot_dim: int,
+    q_norm_weight: Optional[torch.Tensor],
+    kv_norm_weight: torch.Tensor,
+    eps: float,
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor,
+    interleaved: bool,
+    slots: Optional[torch.Tensor],
+    q_latent_out: Optional[torch.Tensor],
+    cache: Optional[torch.Tensor],
+    status: torch.Tensor,
+) -> None:
+    """From a token's product row ``[query latent q_rank | kv latent kv_rank | key part rot_dim]`` (or its
+    float32 split-K partial sums): the RMS-normed query latent into ``q_latent_out [tokens, q_rank]``, and
+    the cache row ``[normed kv latent | rotated key part]`` into the page slot of the token (``cache``
+    ``[pages, 1, page_size, kv_rank + rot_dim]``; ``slots`` None writes none).  Norms carry a weight and
+    ``eps`` inside the root; everything is computed in 32-bit and rounded once."""
+    tokens = down.shape[-2]
+    width = q_rank + kv_rank + rot_dim
+    splits, stride = _maybe_split(down, tokens, width, "down")
+    if inv_freq.shape[0] * 2 != rot_dim:
+        raise ValueError(f"{rot_dim} rotated dimensions need {rot_dim // 2} frequencies, got {inv_freq.shape[0]}")
+    if width * 4 > 48 * 1024:
+        raise UnsupportedSize(f"latent rows of {width} values exceed the kernel's shared memory")
+    page_size = num_pages = 0
+    cache_ptr = 0
+    dtype_of = q_latent_out if q_latent_out is not None else cache
+    if slots is not None:
+        if cache is None or cache.shape[1] != 1 or cache.shape[3] != kv_rank + rot_dim:
+            raise ValueError(f"the latent cache must be [pages, 1, page, {kv_rank + rot_dim}]")
+        num_pages, _, page_size, _ = cache.shape
+        cache_ptr = _dev(cache, "cache")
+    if q_rank and (q_latent_out is None or q_latent_out.shape != (tokens, q_rank) or q_norm_weight is None):
+        raise ValueError("a query latent needs its norm weight and q_latent_out [tokens, q_rank]")
+    fn = _fn(
+        "einf_latent_down_store",
+        [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+         c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(down, "down"), _code(down), splits, stride, _code(dtype_of), tokens, q_rank, kv_rank, rot_dim,
+           _opt(q_norm_weight, "q_norm_weight", torch.float32) if q_rank else 0,
+           _opt(kv_norm_weight, "kv_norm_weight", torch.float32), float(eps),
+           _opt(positions, "positions", torch.int32), _opt(inv_freq, "inv_freq", torch.float32),
+           1 if interleaved else 0, _opt(slots, "slots", torch.int32) if cache_ptr else 0,
+           _dev(q_latent_out, "q_latent_out") if q_rank else 0, cache_ptr, page_size, num_pages,
+           _dev(status, "status"), _stream()),
+        "latent_down_store",
+    )
+
+
+def latent_q_store(
+    q: torch.Tensor,
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor,
+    interleaved: bool,
+    q_plain: torch.Tensor,
+    q_full: torch.Tensor,
+) -> None:
+    """Queries ``[tokens, heads * (dim + rot_dim)]`` (or partial sums), head by head ``[dim plain | rot_dim
+    to rotate]``: the plain part into ``q_plain [tokens, heads, dim]``, the rotated part into the last
+    ``rot_dim`` elements of every head of ``q_full [tokens, heads, kv_rank + rot_dim]``."""
+    tokens, heads, dim = q_plain.shape
+    rot_dim = 2 * inv_freq.shape[0]
+    kv_rank = q_full.shape[2] - rot_dim
+    if q_full.shape[:2] != (tokens, heads) or kv_rank <= 0 or q_full.dtype != q_plain.dtype:
+        raise ValueError(f"q_full {tuple(q_full.shape)} does not fit q_plain {tuple(q_plain.shape)}")
+    splits, stride = _maybe_split(q, tokens, heads * (dim + rot_dim), "q")
+    fn = _fn(
+        "einf_latent_q_store",
+        [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+         c_void_p, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(q, "q"), _code(q), splits, stride, _code(q_plain), tokens, heads, dim, rot_dim, kv_rank,
+           _opt(positions, "positions", torch.int32), _opt(inv_freq, "inv_freq", torch.float32),
+           1 if interleaved else 0, _dev(q_plain, "q_plain"), _dev(q_full, "q_full"), _stream()),
+        "latent_q_store",
+    )
+
+
+def per_head_project(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, h] = weight[h] @ x[t, h]`` for every head: ``x`` and ``out`` are ``[tokens, heads, *]`` views
+    with unit stride in their last dimension (slices of wider rows are fine), ``weight`` is
+    ``[heads, out, in]``.  bfloat16 goes to the library's batched product, everything else to the FMA
+    kernel head by head."""
+    tokens, heads, size_in = x.shape
+    if weight.shape[0] != heads or weight.shape[2] != size_in or out.shape != (tokens, heads, weight.shape[1]):
+        raise ValueError(f"per_head_project: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        if not x.is_cuda:
+            raise KernelError("per_head_project operands must be on a CUDA device: there is no CPU path")
+        torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    for head in range(heads):
+        gemm_simt(x[:, head], weight[head], None, out[:, head])
+
+
+# ---------------------------------------------------------------------------
+# Routed feed-forward
+ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def router_topk(logits: torch.Tensor, top_k: int, score: str, renormalise: bool, expert_ids: torch.Tensor,
+                weights: torch.Tensor) -> None:
+    """Per row of float32 ``logits [tokens, experts]``: the ``top_k`` experts with the largest logits
+    (ties to the lower index) into ``expert_ids`` (int32) and their weights into ``weights`` (float32),
+    both ``[tokens, top_k]``, best first.  A weight is ``sigmoid(z)`` or the softmax over all experts;
+    ``renormalise`` divides the chosen weights by their sum."""
+    tokens, experts = logits.shape
+    if logits.dtype != torch.float32 or weights.dtype != torch.float32 or expert_ids.dtype != torch.int32:
+        raise TypeError("router_topk takes float32 logits and weights and int32 expert ids")
+    if expert_ids.shape != (tokens, top_k) or weights.shape != (tokens, top_k):
+        raise ValueError("expert_ids and weights must be [tokens, top_k]")
+    if not 0 < top_k <= experts or experts > 1024:
+        raise UnsupportedSize(f"top_k {top_k} of {experts} experts (at most 1024)")
+    fn = _fn("einf_router_topk", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(
+        fn(_dev(logits, "logits"), tokens, experts, top_k, ROUTER_SCORES[score], 1 if renormalise else 0,
+           _dev(expert_ids, "expert_ids"), _dev(weights, "weights"), _stream()),
+        "router_topk",
+    )
+
+
+def moe_dispatch(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int,
+                 scale_rows: bool, work: torch.Tensor, place: torch.Tensor, sorted_x: torch.Tensor) -> torch.Tensor:
+    """Sort the (token, choice) pairs by expert.  ``work`` (int32 ``[3 experts + 1]``) gets counts, running
+    cursors and offsets; ``place [tokens, top_k]`` the row of each pair in the sorted order; ``sorted_x
+    [tokens * top_k, hidden]`` the tokens' rows in that order, times the pair's weight with
+    ``scale_rows``.  Returns the offsets ``[experts + 1]`` (a view of ``work``)."""
+    tokens, hidden = x.shape
+    top_k = expert_ids.shape[1]
+    if work.dtype != torch.int32 or work.numel() != 3 * num_experts + 1 or place.dtype != torch.int32:
+        raise ValueError("work must be int32 [3 experts + 1] and place int32")
+    if place.shape != (tokens, top_k) or sorted_x.shape != (tokens * top_k, hidden) or sorted_x.dtype != x.dtype:
+        raise ValueError("place must be [tokens, top_k] and sorted_x [tokens * top_k, hidden] of x's dtype")
+    fn = _fn(
+        "einf_moe_dispatch",
+        [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(x, "x"), _code(x), _opt(expert_ids, "expert_ids", torch.int32), _opt(weights, "weights", torch.float32),
+           tokens, top_k, num_experts, hidden, 1 if scale_rows else 0, _dev(work, "work"), _dev(place, "place"),
+           _dev(sorted_x, "sorted_x"), _stream()),
+        "moe_dispatch",
+    )
+    return work[2 * num_experts:]
+
+
+def moe_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[p] = weight[e] @ x[p]`` for the rows ``offsets[e] <= p < offsets[e + 1]`` of every expert e:
+    ``x [rows, k]`` sorted by expert, ``weight [experts, n, k]``, ``out [rows, n]``."""
+    rows, k = x.shape
+    experts, n, k2 = weight.shape
+    if k2 != k or out.shape != (rows, n) or offsets.numel() != experts + 1 or offsets.dtype != torch.int32:
+        raise ValueError(f"moe_gemm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if not offsets.is_cuda:
+        raise KernelError("moe_gemm operands must be on a CUDA device: there is no CPU path")
+    fn = _fn("einf_moe_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p])
+    _check(
+        fn(_dev(x, "x"), _code(x), _dev(weight, "weight"), _code(weight), offsets.data_ptr(), _dev(out, "out"),
+           _code(out), rows, experts, n, k, _stream()),
+        "moe_gemm",
+    )
+
+
+def moe_combine(y: torch.Tensor, expert_ids: torch.Tensor, place: torch.Tensor, weights: torch.Tensor,
+                scale_outputs: bool, addend: Optional[torch.Tensor], out: torch.Tensor, num_experts: int) -> None:
+    """``out[t] = addend[t] + sum_j y[place[t, j]]`` (times ``weights[t, j]`` with ``scale_outputs``) as
+    float32: the experts' outputs of every token added up in the order of its choices, after the
+    ``addend`` (``[tokens, hidden]`` or float32 partial sums ``[splits, tokens, hidden]``; may be None)."""
+    tokens, hidden = out.shape
+    top_k = expert_ids.shape[1]
+    if out.dtype != torch.float32 or y.shape != (tokens * top_k, hidden):
+        raise ValueError("moe_combine: out must be float32 [tokens, hidden] and y [tokens * top_k, hidden]")
+    splits, stride, addend_code, addend_ptr = 1, 0, FLOAT32, 0
+    if addend is not None:
+        splits, stride = _maybe_split(addend, tokens, hidden, "addend")
+        splits = max(splits, 1)
+        addend_code, addend_ptr = _code(addend), _dev(addend, "addend")
+    fn = _fn(
+        "einf_moe_combine",
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int,
+         c_int, c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(_dev(y, "y"), _code(y), _opt(expert_ids, "expert_ids", torch.int32), _opt(place, "place", torch.int32),
+           _opt(weights, "weights", torch.float32), 1 if scale_outputs else 0, addend_ptr, addend_code, splits, stride,
+           _dev(out, "out"), tokens, int(num_experts), top_k, hidden, _stream()),
+        "moe_combine",
+    )
+
+
+def softcap(values: torch.Tensor, cap: float) -> None:
+    """``values = cap * tanh(values / cap)`` in place (float32)."""
+    if values.dtype != torch.float32:
+        raise TypeError("softcap takes float32 values")
+    fn = _fn("einf_softcap", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(fn(_dev(values, "values"), values.numel(), float(cap), _stream()), "softcap")
 
 
 def _rows_of(x: torch.Tensor, name: str) -> int:

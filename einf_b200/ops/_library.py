@@ -35,6 +35,13 @@ LAUNCHERS = {
     "einf_paged_decode_attention_tcgen05": "attention_tcgen05",
     "einf_paged_prefill_attention_tcgen05_max_clusters": "attention_tcgen05",
     "einf_paged_decode_attention_tcgen05_max_clusters": "attention_tcgen05",
+    "einf_latent_down_store": "latent",
+    "einf_latent_q_store": "latent",
+    "einf_router_topk": "routed",
+    "einf_moe_dispatch": "routed",
+    "einf_moe_gemm": "routed",
+    "einf_moe_combine": "routed",
+    "einf_softcap": "pointwise",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
     "einf_report": "sampling",

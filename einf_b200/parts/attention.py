@@ -8,6 +8,12 @@ itself through the cache (``qwen.py:405-411``); query head ``h`` uses key/value
 head ``h // (heads / kv_heads)``; scores are scaled by ``scale`` and masked
 lower-right causal (``model_runner.py:145``), optionally to the last ``window``
 keys; then the output projection (``qwen.py:360,489``).
+
+Optional, each from the spec: heads of unit root mean square, a soft cap on the scores, a chunked
+mask, keys of another layer, values of another size than keys, a window that also keeps the first
+``keep_first`` positions of the sequence, a rotation with neighbouring dimensions paired, and
+``value_mix``: the first such layer of a model ("source") leaves its values of the step in
+``ctx.extras``, every later one ("blend") caches ``(1 - m) v + m v_source`` with its stored scalar.
 """
 from __future__ import annotations
 
@@ -39,6 +45,8 @@ class PagedAttention(Mixer):
                 specs["v_proj.bias"] = TensorSpec((kv_heads * value_size,), "bias")
         if spec.get("out_bias", False):
             specs["o_proj.bias"] = TensorSpec((hidden,), "bias")
+        if spec.get("value_mix"):
+            specs["value_mix"] = TensorSpec((), "fraction")   # stored by the source layer too, unused there
         return specs
 
     @staticmethod
@@ -48,6 +56,8 @@ class PagedAttention(Mixer):
             spec.get("qk_unit_eps") is not None or spec.get("softcap") or spec.get("chunk")
             or spec.get("shared_kv", False)
             or (spec.get("value_head_size") or spec["head_size"]) != spec["head_size"]
+            or spec.get("keep_first") or spec.get("value_mix")
+            or spec["position"].get("layout", "halves") != "halves"
         )
 
     @staticmethod
@@ -55,7 +65,8 @@ class PagedAttention(Mixer):
         """A general layer still runs the tcgen05 attention kernels (which know the chunked mask and
         the soft cap) when its keys and values have one size that those kernels take."""
         size = int(spec["head_size"])
-        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128)
+        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128) \
+            and not spec.get("keep_first")
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
@@ -94,10 +105,10 @@ class PagedAttention(Mixer):
                 raise ops.UnsupportedSize(
                     f"head sizes {self.head_size}, {self.value_size}: the attention kernels take up to {ops.MAX_HEAD_SIZE}"
                 )
-            if spec["position"].kind != "none":
+            if spec["position"].kind not in ("none", "rope"):
                 raise ValueError(
-                    "an attention layer with unit-norm heads, a soft cap, a chunked mask, shared keys or values of "
-                    f"another size runs without a position encoding here, not with {spec['position'].kind!r}"
+                    "the general attention layer rotates or leaves its heads as they are; it does not know the "
+                    f"position encoding {spec['position'].kind!r}"
                 )
         elif self.head_size % 16 or self.head_size > ops.MAX_HEAD_SIZE:
             raise ops.UnsupportedSize(
@@ -118,12 +129,19 @@ class PagedAttention(Mixer):
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
         self.out_bias = runtime.vector(tensors["o_proj.bias"]) if spec.get("out_bias", False) else None
         self.position = build_nested("position", spec["position"], tensors, runtime)
+        self.keep_first = int(spec.get("keep_first") or 0)
+        if self.keep_first and self.window is None:
+            raise ValueError("keep_first needs a window")
+        self.value_mix = spec.get("value_mix")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix must be source or blend, got {self.value_mix!r}")
+        self.mix = runtime.vector(tensors["value_mix"].reshape(1)) if self.value_mix else None
         self.fast = not self.general and ops.has_fast_attention(runtime.dtype, self.head_size)
         self.general_fast = self.general and self._general_on_tensor_cores(spec, runtime.dtype)
 
     def cache_need(self):
         value = self.value_size if self.value_size != self.head_size else None
-        return PagedKVNeed(self.num_kv_heads, self.head_size, self.window, value)
+        return PagedKVNeed(self.num_kv_heads, self.head_size, self.window, value, self.keep_first)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         tokens = x.shape[0]
@@ -132,11 +150,22 @@ class PagedAttention(Mixer):
         q = torch.empty((tokens, self.num_heads, self.head_size), dtype=dtype, device=device)
         if self.general:
             writes = cache.writes and cache.k is not None and not self.shared_kv
+            shared_values = None
+            if self.value_mix == "source":
+                shared_values = torch.empty((tokens, self.num_kv_heads * self.value_size), dtype=torch.float32,
+                                            device=device)
+                ctx.extras["mixed_values"] = shared_values
+            elif self.value_mix == "blend":
+                shared_values = ctx.extras.get("mixed_values")
+                if shared_values is None:
+                    raise RuntimeError("a layer blends its values before any layer of the step has left its own")
             ops.qkv_norm_store(
                 qkv, self.qkv_bias, ctx.slots[cache.group] if writes else None, q,
                 cache.k if writes else None, cache.v if writes else None, self.num_heads,
                 0 if self.shared_kv else self.num_kv_heads, self.head_size, self.value_size, self.qk_unit_eps,
-                ctx.status,
+                ctx.status, positions=ctx.positions, inv_freq=self.position.inv_freq,
+                interleaved=getattr(self.position, "interleaved", False), value_mix=self.value_mix,
+                shared_values=shared_values, mix=self.mix,
             )
         else:
             self.position.encode_and_store(
@@ -188,4 +217,5 @@ class PagedAttention(Mixer):
         ops.paged_attention_generic(
             q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.seq_of_token, ctx.positions,
             out, self.scale, self.window, ctx.status, chunk=self.chunk, softcap=self.softcap,
+            keep_first=self.keep_first,
         )

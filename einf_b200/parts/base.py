@@ -91,8 +91,11 @@ class PagedKVNeed:
     num_kv_heads: int
     head_size: int
     window: Optional[int] = None
-    #: size of a value head where it differs from the key head's (None: the same)
+    #: size of a value head where it differs from the key head's (None: the same; 0: no value cache,
+    #: the mixer reads its values out of the key rows)
     value_head_size: Optional[int] = None
+    #: with a window: the first that many positions of a sequence stay visible (and cached) too
+    keep_first: int = 0
 
     @property
     def value_size(self) -> int:

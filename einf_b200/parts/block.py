@@ -73,5 +73,24 @@ class PreNormMixerBlock(PreNormBlock):
         return self.mixer.forward(x, ctx, cache)
 
 
+@register_part("block", "parallel")
+class ParallelBlock(PreNormBlock):
+    """``h += mixer(n) + feed_forward(n)`` with one norm ``n = norm(h)`` that both sublayers read.
+    A feed-forward that takes an addend sums both in its last kernel, in 32-bit; otherwise the
+    pending value is the stack of both as float32 terms, which the next norm adds up."""
+
+    @classmethod
+    def part_categories(cls):
+        return {"mixer_norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    def forward(self, residual, pending, ctx, cache):
+        x = self._normalise(self.mixer_norm, pending, residual, ctx)
+        mixed = self.mixer.forward(x, ctx, cache)
+        if getattr(self.feed_forward, "takes_addend", False):
+            return self.feed_forward.forward(x, ctx, add=mixed)   # its last kernel adds the two up
+        terms = [mixed if mixed.dim() == 3 else mixed[None], self.feed_forward.forward(x, ctx)[None]]
+        return torch.cat([term.to(torch.float32) for term in terms], dim=0)
+
+
 def build_block(layer_spec, tensors, runtime) -> Block:
     return part_class("block", layer_spec.block)(layer_spec, tensors, runtime)

@@ -47,12 +47,18 @@ class LinearHead(Part):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
-        return ("gemm_simt",) + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
+        return ("gemm_simt",) + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()) + \
+            (("pointwise",) if spec.get("softcap") else ())
 
     def __init__(self, spec, tensors, runtime, tied=None):
         super().__init__(spec, tensors, runtime)
         self.vocab_size = int(spec["vocab_size"])
         self.weight = tied if tied is not None else runtime.matrix(tensors["weight"])
+        #: ``softcap`` c: logits become ``c * tanh(logits / c)``
+        self.softcap = float(spec["softcap"]) if spec.get("softcap") else None
 
     def forward(self, x: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
-        return ops.project(x, self.weight, status, out_dtype=torch.float32, allow_partial=False)
+        logits = ops.project(x, self.weight, status, out_dtype=torch.float32, allow_partial=False)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
+        return logits

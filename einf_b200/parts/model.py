@@ -110,9 +110,11 @@ class DecoderModel:
                 if owner != index:
                     group = entries[owner].group
                 else:
-                    if need.window not in windows:
-                        windows.append(need.window)
-                    group = windows.index(need.window)
+                    # a window that keeps first positions holds all its pages for now
+                    window = None if need.keep_first else need.window
+                    if window not in windows:
+                        windows.append(window)
+                    group = windows.index(window)
             entries.append(EntryCache(need, owner, group))
         if not windows:
             windows.append(None)  # the manager always has one page group

@@ -8,9 +8,18 @@ in 32-bit (``src/einf/executors/torch/model_runner.py:42-78``).  The table of
 inverse frequencies is made on the host by the reference's own expression, so
 that angles agree with a host computation bit for bit.
 
+With ``layout: "interleaved"`` pair i is dimensions (2i, 2i + 1) instead of (i, i + rotary_dim/2);
+the general store kernel of the attention mixer rotates that layout.  With ``scaling`` (``factor``,
+``low``, ``high``, ``original``) a frequency f of wavelength l = 2 pi / f stays as it is where
+l < original / high, becomes f / factor where l > original / low, and between the two is
+``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``: long wavelengths are
+stretched, short ones kept.
+
 ``none``: no encoding; bias and the cache write only.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -53,12 +62,38 @@ class RotaryPosition(PositionEncoding):
         self.theta = float(spec["theta"])
         if self.rotary_dim % 2:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even")
-        inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim))
+        self.layout = str(spec.get("layout", "halves"))
+        if self.layout not in ("halves", "interleaved"):
+            raise ValueError(f"rotary layout must be halves or interleaved, got {self.layout!r}")
+        self.interleaved = self.layout == "interleaved"
+        scaling = spec.get("scaling")
+        if scaling is None:
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim))
+        else:
+            inv_freq = self.scaled_frequencies(self.theta, self.rotary_dim, scaling)
         self.inv_freq = inv_freq.to(runtime.device)
+
+    @staticmethod
+    def scaled_frequencies(theta: float, rotary_dim: int, scaling) -> torch.Tensor:
+        """The frequency table with wavelength-dependent scaling, made in 64-bit on the host."""
+        factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        table = []
+        for i in range(rotary_dim // 2):
+            f = theta ** (-2.0 * i / rotary_dim)
+            wavelength = 2.0 * math.pi / f
+            if wavelength > original / low:
+                f = f / factor
+            elif wavelength >= original / high:
+                blend = (original / wavelength - low) / (high - low)
+                f = (1.0 - blend) * f / factor + blend * f
+            table.append(f)
+        return torch.tensor(table, dtype=torch.float64).to(torch.float32)
 
     def encode_and_store(self, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size):
         if self.rotary_dim > head_size:
             raise ValueError(f"rotary_dim {self.rotary_dim} exceeds head size {head_size}")
+        if self.interleaved:
+            raise ValueError("the interleaved layout is rotated by the attention mixer's general store kernel")
         _store(self.inv_freq, qkv, bias, ctx, cache, q_out, num_heads, num_kv_heads, head_size)
 
 

@@ -1,0 +1,87 @@
+"""A routed feed-forward: many small gated feed-forwards (experts) of which each token uses a few.
+
+``routed_mlp``: router logits ``z = W_router x`` in 32-bit; the ``top_k`` experts with the largest
+scores (``score``: ``sigmoid`` or ``softmax`` over all experts; ``renormalise`` divides the chosen
+weights by their sum); an expert is ``down(silu(gate(u)) * up(u))`` without biases.  With
+``weight_on: "input"`` the expert sees ``u = w x`` and its output is added as it is; with ``"output"``
+it sees x and its output is multiplied by w.
+
+The tokens never go through the host: the (token, choice) pairs are sorted by expert on the device,
+the two products run over the sorted rows expert by expert in one launch each, and one kernel adds
+a token's expert outputs up in 32-bit, together with another branch's output when the layer runs
+its mixer and its feed-forward side by side (``forward(..., add=...)``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.specs import TensorSpec
+from .base import FeedForward, register_part
+
+
+@register_part("feed_forward", "routed_mlp")
+class RoutedMLP(FeedForward):
+    #: ``forward`` takes ``add``: a tensor (or split-K partial sums) that joins the sum over the experts
+    takes_addend = True
+
+    @classmethod
+    def tensor_specs(cls, spec):
+        hidden, inter, experts = spec["hidden_size"], spec["intermediate_size"], spec["num_experts"]
+        specs = {"router.weight": TensorSpec((experts, hidden))}
+        for e in range(experts):
+            specs[f"experts.{e}.gate_proj.weight"] = TensorSpec((inter, hidden))
+            specs[f"experts.{e}.up_proj.weight"] = TensorSpec((inter, hidden))
+            specs[f"experts.{e}.down_proj.weight"] = TensorSpec((hidden, inter))
+        return specs
+
+    @classmethod
+    def kernel_libraries(cls, spec, runtime):
+        return ("pointwise", "routed", "gemm_simt") + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.hidden_size = int(spec["hidden_size"])
+        self.intermediate_size = int(spec["intermediate_size"])
+        self.num_experts = int(spec["num_experts"])
+        self.top_k = int(spec["top_k"])
+        self.score = str(spec.get("score", "softmax"))
+        if self.score not in ops.ROUTER_SCORES:
+            raise ValueError(f"router score must be one of {sorted(ops.ROUTER_SCORES)}, got {self.score!r}")
+        self.renormalise = bool(spec.get("renormalise", False))
+        weight_on = str(spec.get("weight_on", "output"))
+        if weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on must be input or output, got {weight_on!r}")
+        self.weight_on_input = weight_on == "input"
+        if not 0 < self.top_k <= self.num_experts:
+            raise ValueError(f"top_k {self.top_k} of {self.num_experts} experts")
+        self.router_weight = runtime.matrix(tensors["router.weight"])
+        names = range(self.num_experts)
+        self.gate_up_weight = runtime.matrix(torch.stack([
+            torch.cat([tensors[f"experts.{e}.gate_proj.weight"], tensors[f"experts.{e}.up_proj.weight"]], dim=0)
+            for e in names
+        ]))
+        self.down_weight = runtime.matrix(torch.stack([tensors[f"experts.{e}.down_proj.weight"] for e in names]))
+
+    def forward(self, x, ctx, add=None):
+        tokens = x.shape[0]
+        dtype, device = self.runtime.dtype, x.device
+        experts, top_k = self.num_experts, self.top_k
+        logits = ops.project(x, self.router_weight, ctx.status, out_dtype=torch.float32, allow_partial=False)
+        expert_ids = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+        weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
+        ops.router_topk(logits, top_k, self.score, self.renormalise, expert_ids, weights)
+        work = torch.empty((3 * experts + 1,), dtype=torch.int32, device=device)
+        place = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+        rows = tokens * top_k
+        sorted_x = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
+        offsets = ops.moe_dispatch(x, expert_ids, weights, experts, self.weight_on_input, work, place, sorted_x)
+        gate_up = torch.empty((rows, 2 * self.intermediate_size), dtype=dtype, device=device)
+        ops.moe_gemm(sorted_x, self.gate_up_weight, offsets, gate_up)
+        hidden = torch.empty((rows, self.intermediate_size), dtype=dtype, device=device)
+        ops.silu_mul(gate_up, hidden)
+        y = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
+        ops.moe_gemm(hidden, self.down_weight, offsets, y)
+        out = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=device)
+        ops.moe_combine(y, expert_ids, place, weights, not self.weight_on_input, add, out, experts)
+        return out

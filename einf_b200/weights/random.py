@@ -53,6 +53,8 @@ def random_tensors(
         elif spec.role == "dt_bias":       # softplus of it lies between 0.001 and 0.1
             step = torch.exp(torch.sigmoid(values) * 4.6 - 6.9)
             values = step + torch.log(-torch.expm1(-step))
+        elif spec.role == "fraction":      # a blending weight between 0 and 1
+            values = torch.sigmoid(values)
         elif spec.role == "a_log":         # the logarithm of a rate between 1 and 16
             values = torch.log(1.0 + 15.0 * torch.sigmoid(values))
         else:

@@ -95,7 +95,7 @@ def project(x, weight, status, out_dtype=None, allow_partial=True):
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status,
-                            chunk=None, softcap=None):
+                            chunk=None, softcap=None, keep_first=0, values_in_keys=None):
     tokens, num_heads, head_size = q.shape
     _, num_kv_heads, page_size, _ = k_cache.shape
     groups = num_heads // num_kv_heads
@@ -106,10 +106,12 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         if chunk:
             lo = max(lo, pos // chunk * chunk)
         keys = torch.arange(lo, pos + 1, device=q.device)
+        if window and keep_first:
+            keys = torch.cat([torch.arange(0, min(keep_first, lo), device=q.device), keys])
         pages = block_table[r, (keys // page_size).long()].long()
         offsets = (keys % page_size).long()
         k = k_cache[pages, :, offsets, :].float()      # [n, kv_heads, D]
-        v = v_cache[pages, :, offsets, :].float()
+        v = k[..., :values_in_keys] if values_in_keys else v_cache[pages, :, offsets, :].float()
         k = k.repeat_interleave(groups, dim=1)
         v = v.repeat_interleave(groups, dim=1)
         scores = torch.einsum("hd,nhd->hn", q[t].float(), k) * scale
@@ -139,8 +141,25 @@ def activation(x, out, kind):
     out.copy_(y.to(out.dtype))
 
 
+def _rotate(x, positions, inv_freq, interleaved):
+    """x [T, heads, D]: rotate the first 2n dims, pair i = (i, i + n) or (2i, 2i + 1)."""
+    n = inv_freq.shape[0]
+    if not n:
+        return x
+    angles = positions.float()[:, None] * inv_freq.float()[None, :]
+    cos, sin = angles.cos()[:, None, :], angles.sin()[:, None, :]
+    index = torch.arange(n, device=x.device)
+    first, second = (2 * index, 2 * index + 1) if interleaved else (index, index + n)
+    u, v = x[..., first], x[..., second]
+    out = x.clone()
+    out[..., first] = u * cos - v * sin
+    out[..., second] = v * cos + u * sin
+    return out
+
+
 def qkv_norm_store(qkv, bias, slots, q_out, k_cache, v_cache, num_heads, num_kv_heads, key_size, value_size,
-                   unit_eps, status):
+                   unit_eps, status, positions=None, inv_freq=None, interleaved=False, value_mix=None,
+                   shared_values=None, mix=None):
     values = _summed(qkv)
     tokens = values.shape[0]
     if bias is not None:
@@ -152,6 +171,14 @@ def qkv_norm_store(qkv, bias, slots, q_out, k_cache, v_cache, num_heads, num_kv_
     if unit_eps is not None:
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + unit_eps)
         k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + unit_eps)
+    if inv_freq is not None and inv_freq.shape[0]:
+        q = _rotate(q, positions, inv_freq, interleaved)
+        k = _rotate(k, positions, inv_freq, interleaved)
+    if value_mix == "source":
+        shared_values.copy_(v.reshape(shared_values.shape))
+    elif value_mix == "blend":
+        m = mix.float().reshape(())
+        v = (1 - m) * v + m * shared_values.reshape(v.shape)
     q_out.copy_(q.reshape(q_out.shape).to(q_out.dtype))
     if slots is not None and num_kv_heads:
         page_size = k_cache.shape[2]
@@ -160,6 +187,83 @@ def qkv_norm_store(qkv, bias, slots, q_out, k_cache, v_cache, num_heads, num_kv_
         offset = (slots[keep] % page_size).long()
         k_cache[page, :, offset, :] = k[keep].to(k_cache.dtype)
         v_cache[page, :, offset, :] = v[keep].to(v_cache.dtype)
+
+
+def latent_down_store(down, q_rank, kv_rank, rot_dim, q_norm_weight, kv_norm_weight, eps, positions, inv_freq,
+                      interleaved, slots, q_latent_out, cache, status):
+    values = _summed(down)
+    q_latent, latent, part = values.split([q_rank, kv_rank, rot_dim], dim=-1)
+    if q_rank:
+        q_latent = q_latent * torch.rsqrt(q_latent.pow(2).mean(-1, keepdim=True) + eps) * q_norm_weight
+        q_latent_out.copy_(q_latent.to(q_latent_out.dtype))
+    latent = latent * torch.rsqrt(latent.pow(2).mean(-1, keepdim=True) + eps) * kv_norm_weight
+    part = _rotate(part[:, None, :], positions, inv_freq, interleaved)[:, 0]
+    if slots is not None:
+        page_size = cache.shape[2]
+        keep = slots >= 0
+        page = (slots[keep] // page_size).long()
+        offset = (slots[keep] % page_size).long()
+        cache[page, 0, offset, :] = torch.cat([latent, part], dim=-1)[keep].to(cache.dtype)
+
+
+def latent_q_store(q, positions, inv_freq, interleaved, q_plain, q_full):
+    tokens, heads, dim = q_plain.shape
+    rot_dim = 2 * inv_freq.shape[0]
+    values = _summed(q).reshape(tokens, heads, dim + rot_dim)
+    q_plain.copy_(values[..., :dim].to(q_plain.dtype))
+    q_full[..., q_full.shape[2] - rot_dim:] = _rotate(values[..., dim:], positions, inv_freq, interleaved).to(q_full.dtype)
+
+
+def per_head_project(x, weight, out):
+    out.copy_(torch.einsum("thi,hoi->tho", x.float(), weight.float()).to(out.dtype))
+
+
+def router_topk(logits, top_k, score, renormalise, expert_ids, weights):
+    z = logits.float()
+    order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
+    chosen = torch.gather(scores, 1, order)
+    if renormalise:
+        chosen = chosen / chosen.sum(-1, keepdim=True)
+    expert_ids.copy_(order.to(expert_ids.dtype))
+    weights.copy_(chosen)
+
+
+def moe_dispatch(x, expert_ids, weights, num_experts, scale_rows, work, place, sorted_x):
+    tokens, top_k = expert_ids.shape
+    flat = expert_ids.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices          # sorted row -> pair
+    counts = torch.bincount(flat, minlength=num_experts)
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int32, device=x.device)
+    offsets[1:] = counts.cumsum(0).to(torch.int32)
+    work[2 * num_experts:] = offsets
+    rows = torch.empty_like(flat)
+    rows[order] = torch.arange(flat.shape[0], device=x.device)
+    place.copy_(rows.reshape(tokens, top_k).to(place.dtype))
+    source = x.float()[(order // top_k)]
+    if scale_rows:
+        source = source * weights.reshape(-1)[order][:, None]
+    sorted_x.copy_(source.to(sorted_x.dtype))
+    return work[2 * num_experts:]
+
+
+def moe_gemm(x, weight, offsets, out):
+    for e in range(weight.shape[0]):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        if hi > lo:
+            out[lo:hi] = (x[lo:hi].float() @ weight[e].float().T).to(out.dtype)
+
+
+def moe_combine(y, expert_ids, place, weights, scale_outputs, addend, out, num_experts):
+    total = torch.zeros_like(out) if addend is None else _summed(addend).clone()
+    for j in range(expert_ids.shape[1]):
+        term = y.float()[place[:, j].long()]
+        total = total + (weights[:, j, None] * term if scale_outputs else term)
+    out.copy_(total)
+
+
+def softcap(values, cap):
+    values.copy_(cap * torch.tanh(values / cap))
 
 
 def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, out, dt_raw=None, dt_bias=None,
@@ -320,7 +424,8 @@ _NAMES = (
     "embed", "add_rmsnorm", "rope_kv_write", "silu_mul", "linear", "gemm_simt", "project",
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
-    "gated_norm", "recurrence_plan",
+    "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
+    "moe_dispatch", "moe_gemm", "moe_combine", "softcap",
 )
 
 

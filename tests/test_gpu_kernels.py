@@ -1088,9 +1088,9 @@ def test_attention_reports_a_bad_page(dev):
     ops.paged_attention_generic(q, k, v, table, seq, pos, out, scale, None, st)
     assert int(st) == ops.STATUS_BAD_PAGE and torch.isfinite(out).all()
     with pytest.raises(ops.UnsupportedSize):
-        ops.paged_attention_generic(torch.empty(1, 2, 264, device=dev), torch.empty(1, 1, 4, 264, device=dev),
-                                    torch.empty(1, 1, 4, 264, device=dev), table, seq, pos,
-                                    torch.empty(1, 2, 264, device=dev), 1.0, None, st)
+        ops.paged_attention_generic(torch.empty(1, 2, 648, device=dev), torch.empty(1, 1, 4, 648, device=dev),
+                                    torch.empty(1, 1, 4, 648, device=dev), table, seq, pos,
+                                    torch.empty(1, 2, 648, device=dev), 1.0, None, st)
 
 
 def test_kernels_refuse_the_cpu():
