@@ -57,14 +57,16 @@ PYBIND11_MODULE(_control, m) {
       .def("release", &PagePool::release);
 
   py::class_<GroupSpec>(m, "GroupSpec")
-      .def(py::init([](int num_pages, int page_size, int window) {
+      .def(py::init([](int num_pages, int page_size, int window, int keep_first) {
              GroupSpec spec;
              spec.num_pages = num_pages;
              spec.page_size = page_size;
              spec.window = window;
+             spec.keep_first = keep_first;
              return spec;
            }),
-           py::arg("num_pages"), py::arg("page_size"), py::arg("window") = 0)
+           py::arg("num_pages"), py::arg("page_size"), py::arg("window") = 0, py::arg("keep_first") = 0)
+      .def_readonly("keep_first", &GroupSpec::keep_first)
       .def_readonly("num_pages", &GroupSpec::num_pages)
       .def_readonly("page_size", &GroupSpec::page_size)
       .def_readonly("window", &GroupSpec::window);
@@ -214,8 +216,10 @@ PYBIND11_MODULE(_control, m) {
 
   py::class_<PackConfig>(m, "PackConfig")
       .def(py::init([](int page_size, std::vector<int> pages_per_group, std::vector<int> windows, int vocab_size,
-                       int table_width, int max_tokens, int max_requests, int q_tile) {
+                       int table_width, int max_tokens, int max_requests, int q_tile, std::vector<int> keeps) {
              PackConfig c;
+             c.keeps = std::move(keeps);
+             if (!c.keeps.empty() && c.keeps.size() != windows.size()) throw InvalidArgument("one keep_first per cache group");
              c.page_size = page_size;
              c.pages_per_group = std::move(pages_per_group);
              c.windows = std::move(windows);
@@ -228,7 +232,8 @@ PYBIND11_MODULE(_control, m) {
              return c;
            }),
            py::arg("page_size"), py::arg("pages_per_group"), py::arg("windows"), py::arg("vocab_size"),
-           py::arg("table_width"), py::arg("max_tokens"), py::arg("max_requests"), py::arg("q_tile") = 128);
+           py::arg("table_width"), py::arg("max_tokens"), py::arg("max_requests"), py::arg("q_tile") = 128,
+           py::arg("keeps") = std::vector<int>());
 
   py::class_<PackedStep>(m, "PackedStep")
       .def_readonly("total", &PackedStep::total)

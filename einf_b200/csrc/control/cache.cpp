@@ -79,6 +79,7 @@ CacheManager::CacheManager(std::vector<GroupSpec> groups, int num_state_slots)
   for (const GroupSpec& spec : groups_) {
     if (spec.page_size <= 0) throw InvalidArgument("page_size must be positive");
     if (spec.window < 0) throw InvalidArgument("window must not be negative");
+    if (spec.keep_first < 0) throw InvalidArgument("keep_first must not be negative");
     pools_.emplace_back(spec.num_pages);
   }
 }
@@ -105,8 +106,10 @@ std::vector<int> CacheManager::pages_needed(const RequestId& id, int start, int 
     const GroupSpec& spec = groups_[g];
     const int first = first_needed_page(spec, start);
     const int last = (end - 1) / spec.page_size;
+    const int kept = spec.kept_pages();
     int count = 0;
-    for (int page = first; page <= last; ++page) {
+    for (int page = 0; page <= last; ++page) {
+      if (page >= kept && page < first) continue;   // passed by the window and not kept
       const bool have = found != entries_.end() &&
                         page < static_cast<int>(found->second.tables[g].size()) &&
                         found->second.tables[g][page] >= 0;
@@ -125,7 +128,7 @@ bool CacheManager::room_for(int context_len, int portion) const {
     int pages = (tokens + spec.page_size - 1) / spec.page_size;
     if (spec.window > 0 && tokens < context_len) {
       // a window rarely starts on a page edge; but it never spans more pages than the whole context
-      pages = std::min(pages + 1, (context_len + spec.page_size - 1) / spec.page_size);
+      pages = std::min(pages + 1 + spec.kept_pages(), (context_len + spec.page_size - 1) / spec.page_size);
     }
     if (pages > pools_[g].free_count()) return false;
   }
@@ -163,8 +166,10 @@ bool CacheManager::reserve(const RequestId& id, int start, int end, int* short_g
     if (static_cast<int>(table.size()) <= last) table.resize(last + 1, -1);
     std::vector<int> fresh_pages;
     pools_[g].allocate(needed[g], &fresh_pages);
+    const int kept = spec.kept_pages();
     size_t next = 0;
-    for (int page = first; page <= last; ++page) {
+    for (int page = 0; page <= last; ++page) {
+      if (page >= kept && page < first) continue;
       if (table[page] < 0) table[page] = fresh_pages[next++];
     }
   }
@@ -184,7 +189,7 @@ int CacheManager::advance(const RequestId& id, int cached_len) {
     std::vector<int>& table = found->second.tables[g];
     const int whole_pages_passed = std::min<int>(first_needed_key / spec.page_size, static_cast<int>(table.size()));
     std::vector<int> passed;
-    for (int page = 0; page < whole_pages_passed; ++page) {
+    for (int page = spec.kept_pages(); page < whole_pages_passed; ++page) {
       if (table[page] >= 0) {
         passed.push_back(table[page]);
         table[page] = -1;

@@ -74,6 +74,9 @@ struct GroupSpec {
   int num_pages = 0;
   int page_size = 0;
   int window = 0;  // 0: every key is kept; n > 0: only the last n keys are needed
+  int keep_first = 0;  // with a window: the first n positions of a sequence stay needed too
+  // Pages at the head of a sequence that a window never passes.
+  int kept_pages() const { return window > 0 && keep_first > 0 ? (keep_first + page_size - 1) / page_size : 0; }
 };
 
 // ---------------------------------------------------------------------------
@@ -233,6 +236,7 @@ struct PackConfig {
   int page_size = 0;
   std::vector<int> pages_per_group;
   std::vector<int> windows;       // 0: all keys
+  std::vector<int> keeps;         // per group: first positions a window keeps (empty: none)
   int vocab_size = 0;
   int table_width = 0;
   int max_tokens = 0;

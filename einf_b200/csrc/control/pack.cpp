@@ -142,8 +142,10 @@ PackedStep pack_step(const std::vector<ScheduledRequest>& requests, const std::v
       }
       const int window = config.windows[g];
       const int first_key = window > 0 ? std::max(0, start - window + 1) : 0;
-      for (int p = first_key / page; p < needed_pages; ++p)
-        if (table[p] < 0)
+      const int keep = window > 0 && g < static_cast<int>(config.keeps.size()) ? config.keeps[g] : 0;
+      const int kept_pages = keep > 0 ? (keep + page - 1) / page : 0;
+      for (int p = 0; p < needed_pages; ++p)
+        if ((p < kept_pages || p >= first_key / page) && table[p] < 0)
           throw InvalidArgument(where + ": a page it needs in group " + std::to_string(g) +
                                 " is missing from its block table");
       for (int t = 0; t < q_len; ++t) {

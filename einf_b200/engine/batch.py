@@ -67,13 +67,14 @@ class StepInputBuilder:
         table_width: int,
         max_tokens: int,
         max_requests: int,
+        group_keeps: Optional[Sequence[int]] = None,
     ) -> None:
         self.device = torch.device(device)
         self.table_width = table_width
         self.groups = len(pages_per_group)
         self.config = PackConfig(
             page_size, list(pages_per_group), [int(w or 0) for w in group_windows], vocab_size, table_width,
-            max_tokens, max_requests, Q_TILE,
+            max_tokens, max_requests, Q_TILE, [int(k or 0) for k in (group_keeps or [0] * len(pages_per_group))],
         )
         capacity = step_buffer_size(
             max_tokens, max_requests, max_tokens, self.groups, table_width, max_tokens, max_requests

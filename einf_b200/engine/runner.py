@@ -74,10 +74,10 @@ class ModelRunner:
         else:
             base_pages = engine_config.num_blocks
         self.pages_per_group = []
-        for window in plan.group_windows:
+        for window, keep in zip(plan.group_windows, plan.group_keeps):
             pages = base_pages
             if window:
-                per_request = -(-(window + engine_config.max_prefill_chunk_len) // page) + 1
+                per_request = -(-(window + engine_config.max_prefill_chunk_len) // page) + 1 + -(-keep // page)
                 pages = min(pages, engine_config.max_requests * per_request)
             self.pages_per_group.append(pages)
         self.page_size = page
@@ -105,6 +105,7 @@ class ModelRunner:
             self.table_width,
             max_tokens=max(engine_config.max_batch_len, engine_config.max_requests),
             max_requests=engine_config.max_requests,
+            group_keeps=plan.group_keeps,
         )
         self.vocab_size = spec.vocab_size
         self.steps = 0
@@ -171,8 +172,9 @@ class ModelRunner:
 
     def group_specs(self) -> list[GroupSpec]:
         return [
-            GroupSpec(pages, self.page_size, int(window or 0))
-            for pages, window in zip(self.pages_per_group, self.model.cache_plan.group_windows)
+            GroupSpec(pages, self.page_size, int(window or 0), int(keep or 0))
+            for pages, window, keep in zip(
+                self.pages_per_group, self.model.cache_plan.group_windows, self.model.cache_plan.group_keeps)
         ]
 
     # ------------------------------------------------------------------

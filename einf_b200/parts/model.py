@@ -63,6 +63,8 @@ class CachePlan:
     entries: tuple[EntryCache, ...]
     #: window of each page group (None: all keys are kept)
     group_windows: tuple[Optional[int], ...]
+    #: per page group: the first positions of a sequence its window keeps (0: none)
+    group_keeps: tuple[int, ...] = ()
 
     @property
     def has_state(self) -> bool:
@@ -90,7 +92,7 @@ class DecoderModel:
         self.cache_plan = self._plan_cache()
 
     def _plan_cache(self) -> CachePlan:
-        windows: list[Optional[int]] = []
+        windows: list[tuple[Optional[int], int]] = []
         entries: list[EntryCache] = []
         for index, entry in enumerate(self.schedule):
             need = self.blocks[entry.layer].mixer.cache_need()
@@ -110,15 +112,15 @@ class DecoderModel:
                 if owner != index:
                     group = entries[owner].group
                 else:
-                    # a window that keeps first positions holds all its pages for now
-                    window = None if need.keep_first else need.window
-                    if window not in windows:
-                        windows.append(window)
-                    group = windows.index(window)
+                    # a group is a window and the first positions it keeps
+                    key = (need.window, need.keep_first if need.window else 0)
+                    if key not in windows:
+                        windows.append(key)
+                    group = windows.index(key)
             entries.append(EntryCache(need, owner, group))
         if not windows:
-            windows.append(None)  # the manager always has one page group
-        return CachePlan(tuple(entries), tuple(windows))
+            windows.append((None, 0))  # the manager always has one page group
+        return CachePlan(tuple(entries), tuple(w for w, _ in windows), tuple(k for _, k in windows))
 
     def forward(self, ctx: StepContext, caches: list[CacheView]) -> torch.Tensor:
         """Run the step's tokens through every schedule entry; float logits ``[S, vocab]``

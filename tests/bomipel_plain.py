@@ -134,10 +134,16 @@ def silu(z):
     return z * torch.sigmoid(z)
 
 
-def routed_feed_forward(h, w, mlp):
+def routed_feed_forward(h, w, mlp, margins=None):
+    """``margins`` (a list) gets, per token, the gap between the last chosen and the best refused
+    router logit: how far the choice is from a close call."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
-    scores = torch.sigmoid(h @ w["router"].T)                           # [T, experts]
+    logits = h @ w["router"].T
+    scores = torch.sigmoid(logits)                                      # [T, experts]
     chosen = torch.topk(scores, top, dim=-1).indices
+    if margins is not None and top < experts:
+        ordered = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -150,7 +156,7 @@ def _sub(weights, prefix):
     return {name[len(prefix):]: t.to(F64) for name, t in weights.items() if name.startswith(prefix)}
 
 
-def forward(config, weights, tokens, start=0):
+def forward(config, weights, tokens, start=0, margins=None):
     """Logits [T, vocab] and the residual stream after every layer [layers, T, width]."""
     eps = float(config["norm"]["eps"])
     positions = torch.arange(start, start + len(tokens))
@@ -167,7 +173,7 @@ def forward(config, weights, tokens, start=0):
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            mixed = mixed + routed_feed_forward(n, _sub(weights, prefix + "mlp."), layer["mlp"])
+            mixed = mixed + routed_feed_forward(n, _sub(weights, prefix + "mlp."), layer["mlp"], margins)
         x = x + mixed
         streams.append(x)
     logits = rms_norm(x, weights["final.norm"].to(F64), eps) @ weights["embed"].to(F64).T
@@ -175,3 +181,59 @@ def forward(config, weights, tokens, start=0):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits, torch.stack(streams)
+
+
+def tensor_shapes(config):
+    """Name -> shape of every tensor a model folder of this configuration holds."""
+    width = config["width"]
+    shapes = {"embed": (config["vocab"], width), "final.norm": (width,)}
+    for index, layer in enumerate(config["layers"]):
+        prefix, m = f"l{index}.", layer["mixer"]
+        shapes[prefix + "norm1"] = (width,)
+        mix = prefix + "mix."
+        if layer["type"] == "attention":
+            shapes[mix + "q"] = (m["heads"] * m["dim"], width)
+            shapes[mix + "k"] = (m["kv_heads"] * m["dim"], width)
+            shapes[mix + "v"] = (m["kv_heads"] * m["vdim"], width)
+            shapes[mix + "o"] = (width, m["heads"] * m["vdim"])
+            if m.get("v_mix"):
+                shapes[mix + "vmix"] = ()
+        else:
+            shapes[mix + "dq"] = (m["q_rank"], width)
+            shapes[mix + "dq.norm"] = (m["q_rank"],)
+            shapes[mix + "uq"] = (m["heads"] * (m["dim"] + m["rot_dim"]), m["q_rank"])
+            shapes[mix + "dkv"] = (m["kv_rank"] + m["rot_dim"], width)
+            shapes[mix + "dkv.norm"] = (m["kv_rank"],)
+            shapes[mix + "uk"] = (m["heads"] * m["dim"], m["kv_rank"])
+            shapes[mix + "uv"] = (m["heads"] * m["vdim"], m["kv_rank"])
+            shapes[mix + "o"] = (width, m["heads"] * m["vdim"])
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            ff = mlp["expert"]["ff"]
+            shapes[prefix + "mlp.router"] = (mlp["router"]["experts"], width)
+            for e in range(mlp["router"]["experts"]):
+                shapes[prefix + f"mlp.e{e}.gate"] = (ff, width)
+                shapes[prefix + f"mlp.e{e}.up"] = (ff, width)
+                shapes[prefix + f"mlp.e{e}.down"] = (width, ff)
+    return shapes
+
+
+def random_model(config, seed):
+    """Random weights in bfloat16: matrices that keep activations of order one (so that scores and
+    router logits spread), norm weights around one, blending weights inside (0, 1)."""
+    generator = torch.Generator().manual_seed(seed)
+    weights = {}
+    for name, shape in sorted(tensor_shapes(config).items()):
+        values = torch.randn(shape, generator=generator)
+        if name.endswith("norm") or name.endswith("norm1"):
+            values = 1.0 + 0.1 * values
+        elif name.endswith("vmix"):
+            values = 0.2 + 0.6 * torch.sigmoid(values)
+        elif name == "embed":
+            pass
+        elif name.endswith("router"):
+            values = values * 2.0 * shape[-1] ** -0.5
+        else:
+            values = values * shape[-1] ** -0.5
+        weights[name] = values.to(torch.bfloat16)
+    return weights

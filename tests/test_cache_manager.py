@@ -72,6 +72,31 @@ def test_window_gives_pages_back_as_it_passes():
     assert manager.free_pages(1) == 5 and manager.free_pages(0) == 16
 
 
+def test_window_that_keeps_the_first_positions_never_gives_their_pages_back():
+    # page 4, window 6, the first 5 positions stay visible: pages 0 and 1 are kept for good
+    manager = CacheManager([GroupSpec(32, 4), GroupSpec(8, 4, window=6, keep_first=5)])
+    assert manager.group(1).keep_first == 5
+    assert manager.reserve("a", 0, 18)
+    assert manager.advance("a", 18) == 1          # next query at 18 sees 13..18: pages 0-2 passed, 0 and 1 are kept
+    assert manager.block_table("a", 1) == [0, 1, -1, 3, 4]
+    for length in range(18, 70):
+        assert manager.reserve("a", length, length + 1)
+        manager.advance("a", length + 1)
+        table = manager.block_table("a", 1)
+        assert table[0] >= 0 and table[1] >= 0
+        assert manager.held_pages(1) <= 2 + 3
+        manager.check_invariants()
+    # a request that comes back after its pages were released needs the kept pages again
+    manager.release("a")
+    assert manager.free_pages(1) == 8
+    assert manager.reserve("b", 0, 3) and manager.block_table("b", 1) == [0]
+    # a portion that starts beyond the kept pages still takes them (nothing of them was ever held)
+    assert manager.pages_needed("c", 20, 22)[1] == 2 + 3   # kept pages 0, 1 and pages 3..5 of keys 15..21
+    # keep_first without a window means nothing
+    plain = CacheManager([GroupSpec(4, 4, window=0, keep_first=3)])
+    assert plain.reserve("a", 0, 16) and plain.advance("a", 16) == 0
+
+
 def test_window_needs_only_what_the_portion_sees():
     manager = CacheManager([GroupSpec(4, 4, window=4)])
     assert manager.reserve("a", 0, 12) is False or True  # 3 pages for 12 tokens of one portion
