@@ -267,6 +267,162 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same product over rows that are sorted by group (the experts of a routed feed-forward):
+// out[r] = W[g] x[r] for offsets[g] <= r < offsets[g + 1], W stacked [groups, n, k].  The grid's y
+// dimension is a list of token tiles that never cross a group: tile slot y belongs to the group
+// and the place that a walk over the offsets gives it (slots beyond the last tile leave at once),
+// so the host never has to know how many rows a group got.  A tile's box of x may reach into the
+// next group's rows (or past the end, where TMA fills zeros): those columns of the accumulator are
+// computed and not stored.  No split-K: the groups already spread a small batch over the GPU.
+// ---------------------------------------------------------------------------
+struct GroupedParams {
+  void* out;              // [rows, n] (out_dtype)
+  const int* offsets;     // [groups + 1], written by a kernel earlier in the step
+  int* status;
+  int rows, n, k, groups;
+  int token_tile;
+  int stages;
+  int out_dtype;
+};
+
+__device__ __forceinline__ bool find_group_tile(const GroupedParams& p, int slot, int* group, int* t0, int* valid) {
+  for (int g = 0; g < p.groups; ++g) {
+    const int begin = p.offsets[g], count = p.offsets[g + 1] - begin;
+    const int tiles = (count + p.token_tile - 1) / p.token_tile;
+    if (slot < tiles) {
+      *group = g;
+      *t0 = begin + slot * p.token_tile;
+      *valid = min(p.token_tile, count - slot * p.token_tile);
+      return true;
+    }
+    slot -= tiles;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                            GroupedParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  const int x_tile_bytes = p.token_tile * kBlockK * 2;
+  const int stage_bytes = kWTileBytes + x_tile_bytes;
+  const uint32_t bar_base = smem_base + p.stages * stage_bytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * kMaxStages);
+  const uint32_t tmem_holder = bar_base + 8u * (2 * kMaxStages + 1);
+  unsigned char* generic_base = smem_raw + (smem_base - smem_addr(smem_raw));
+  volatile uint32_t* tmem_holder_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + p.stages * stage_bytes + 8 * (2 * kMaxStages + 1));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBlockW;
+  const int num_kblocks = (p.k + kBlockK - 1) / kBlockK;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < (uint32_t)p.token_tile) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_holder), "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder_ptr;
+  pdl_launch_dependents();
+
+  // Every role finds the tile by itself, after the wait for the kernel that wrote the offsets.
+  pdl_wait();
+  int group = 0, t0 = 0, valid = 0;
+  const bool have = find_group_tile(p, blockIdx.y, &group, &t0, &valid);
+
+  if (have && warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < num_kblocks && ok; ++i) {
+        const int s = i % p.stages;
+        if (i >= p.stages) ok = mbar_wait(empty_bar(s), ((i / p.stages) & 1) ^ 1, p.status);
+        if (!ok) break;
+        mbar_expect_tx(full_bar(s), stage_bytes);
+        tma_load_2d(smem_base + s * stage_bytes, &map_w, i * kBlockK, group * p.n + n0, full_bar(s));
+        tma_load_2d(smem_base + s * stage_bytes + kWTileBytes, &map_x, i * kBlockK, t0, full_bar(s));
+      }
+    }
+  } else if (have && warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.token_tile >> 3) << 17) |
+                             ((uint32_t)(kBlockW >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < num_kblocks && ok; ++i) {
+        const int s = i % p.stages;
+        ok = mbar_wait(full_bar(s), (i / p.stages) & 1, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t w_desc = umma_desc(smem_base + s * stage_bytes);
+        const uint64_t x_desc = umma_desc(smem_base + s * stage_bytes + kWTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+          const uint32_t step = (uint32_t)(kk * kUmmaK * 2) >> 4;
+          umma_bf16(tmem_base, (w_desc & 0xFFFFFFFF00000000ull) | (uint32_t)((uint32_t)w_desc + step),
+                    (x_desc & 0xFFFFFFFF00000000ull) | (uint32_t)((uint32_t)x_desc + step), idesc,
+                    (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));
+      }
+      umma_commit(accum_bar);
+    }
+  } else if (have) {
+    const bool ok = mbar_wait(accum_bar, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int lane_base = (warp & 3) * 32;
+      const int row = n0 + lane_base + lane;         // weight row of this group = output column
+      const bool row_ok = row < p.n;
+      float* out_f = reinterpret_cast<float*>(p.out);
+      __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(p.out);
+      const bool as_float = p.out_dtype == kFloat32;
+      for (int col0 = 0; col0 < p.token_tile; col0 += 16) {
+        if (col0 >= valid) break;                    // uniform across the warp
+        uint32_t v[16];
+        tmem_load16(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)col0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row_ok) {
+          const int count = min(16, valid - col0);
+          const size_t first = (size_t)(t0 + col0) * p.n + row;
+          if (as_float) {
+            float* dst = out_f + first;
+#pragma unroll
+            for (int c = 0; c < 16; ++c, dst += p.n)
+              if (c < count) *dst = __uint_as_float(v[c]);
+          } else {
+            __nv_bfloat16* dst = out_h + first;
+#pragma unroll
+            for (int c = 0; c < 16; ++c, dst += p.n)
+              if (c < count) *dst = __float2bfloat16_rn(__uint_as_float(v[c]));
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
 }  // namespace einf
 
 using namespace einf;
@@ -364,4 +520,47 @@ extern "C" int einf_gemm_tcgen05_splits(int k, int splits) {
   if (splits > total_kblocks) splits = total_kblocks;
   const int per_split = (total_kblocks + splits - 1) / splits;
   return (total_kblocks + per_split - 1) / per_split;
+}
+
+// The token tile of the grouped product for `rows` rows over `groups` groups: about one and a half
+// times the average rows of a group, a multiple of 16 between 16 and 256.
+extern "C" int einf_gemm_grouped_tcgen05_token_tile(int rows, int groups) {
+  const int average = (rows + groups - 1) / (groups > 0 ? groups : 1);
+  int tile = (average * 3 / 2 + 15) / 16 * 16;
+  return tile < 16 ? 16 : (tile > 256 ? 256 : tile);
+}
+
+// x: [rows, k] bfloat16 contiguous, sorted by group; w: [groups, n, k] bfloat16 contiguous; offsets: [groups + 1]
+// on the device; out: [rows, n] in out_dtype.  k must be a multiple of 8, the base pointers 16-byte aligned.
+extern "C" int einf_gemm_grouped_tcgen05(const void* x, const void* w, const int* offsets, void* out, int out_dtype,
+                                         int rows, int groups, int n, int k, int* status, cudaStream_t stream) {
+  if (rows == 0 || n == 0 || groups == 0) return 0;
+  if (k % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+  const int token_tile = einf_gemm_grouped_tcgen05_token_tile(rows, groups);
+  const int total_kblocks = (k + kBlockK - 1) / kBlockK;
+  int stages = total_kblocks < kMaxStages ? total_kblocks : kMaxStages;
+  while (stages > 3 && smem_bytes(token_tile, stages) > 110 * 1024) --stages;
+  while (stages > 1 && smem_bytes(token_tile, stages) > 200 * 1024) --stages;
+  CUtensorMap map_w, map_x;
+  int rc = make_map(&map_w, w, (long long)groups * n, k, k, kBlockW);
+  if (rc) return rc;
+  rc = make_map(&map_x, x, rows, k, k, token_tile);
+  if (rc) return rc;
+  GroupedParams p;
+  p.out = out;
+  p.offsets = offsets;
+  p.status = status;
+  p.rows = rows;
+  p.n = n;
+  p.k = k;
+  p.groups = groups;
+  p.token_tile = token_tile;
+  p.stages = stages;
+  p.out_dtype = out_dtype;
+  const size_t smem = smem_bytes(token_tile, stages);
+  cudaError_t e = cudaFuncSetAttribute(gemm_grouped_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int slots = (rows + token_tile - 1) / token_tile + (groups < rows ? groups : rows);
+  dim3 grid((n + kBlockW - 1) / kBlockW, slots, 1);
+  return (int)launch_pdl(gemm_grouped_tcgen05_kernel, grid, dim3(kGemmThreads), smem, stream, map_w, map_x, p);
 }

@@ -815,15 +815,28 @@ def moe_dispatch(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tenso
     return work[2 * num_experts:]
 
 
-def moe_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor) -> None:
+def moe_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor,
+             status: Optional[torch.Tensor] = None) -> None:
     """``out[p] = weight[e] @ x[p]`` for the rows ``offsets[e] <= p < offsets[e + 1]`` of every expert e:
-    ``x [rows, k]`` sorted by expert, ``weight [experts, n, k]``, ``out [rows, n]``."""
+    ``x [rows, k]`` sorted by expert, ``weight [experts, n, k]``, ``out [rows, n]``.  bfloat16 operands
+    (with ``status`` for the bounded waits, k a multiple of 8) run on the tcgen05 kernel whose token
+    tiles never cross an expert; everything else, the 32-bit path included, on the FMA kernel."""
     rows, k = x.shape
     experts, n, k2 = weight.shape
     if k2 != k or out.shape != (rows, n) or offsets.numel() != experts + 1 or offsets.dtype != torch.int32:
         raise ValueError(f"moe_gemm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     if not offsets.is_cuda:
         raise KernelError("moe_gemm operands must be on a CUDA device: there is no CPU path")
+    if (status is not None and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and k % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        fn = _fn("einf_gemm_grouped_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_void_p, c_void_p])
+        _check(
+            fn(_dev(x, "x"), _dev(weight, "weight"), offsets.data_ptr(), _dev(out, "out"), _code(out), rows, experts,
+               n, k, _dev(status, "status"), _stream()),
+            "gemm_grouped_tcgen05",
+        )
+        return
     fn = _fn("einf_moe_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_void_p])
     _check(

@@ -11,6 +11,11 @@ The cache holds the row ``[c | r]`` per token: one key/value head of size ``kv_r
 (``q_plain . W_uk[h] c = (W_uk[h]^T q_plain) . c``) and the value up-projection applied after the
 mixing (``sum_j p_j W_uv[h] c_j = W_uv[h] sum_j p_j c_j``), so attention runs on the cached rows as they
 are, with every query head on the one cached head.
+
+Where a cached row has 64 or 128 elements (bfloat16) the tensor-core attention kernels take it as key
+and as value at once: the mixed rows then carry ``rot_dim`` elements more than the value up-projection
+reads (a fifth to a quarter more work in the second product, none in memory traffic).  Other row
+sizes, and the 32-bit path, run the general kernel, which reads the values out of the key rows.
 """
 from __future__ import annotations
 
@@ -41,8 +46,14 @@ class LatentAttention(Mixer):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
+        row = int(spec["kv_rank"]) + int(spec["rotary_size"])
+        fast = (f"attention_tcgen05:HEAD_SIZE={row}",) if cls._row_on_tensor_cores(row, runtime.dtype) else ()
         return ("pointwise", "latent", "attention_generic", "gemm_simt") + \
-            (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
+            (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()) + fast
+
+    @staticmethod
+    def _row_on_tensor_cores(row: int, dtype) -> bool:
+        return dtype == torch.bfloat16 and row in (64, 128)
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -73,6 +84,17 @@ class LatentAttention(Mixer):
         self.k_up_t = runtime.matrix(k_up.transpose(1, 2).contiguous())
         self.v_up = runtime.matrix(tensors["v_up.weight"].reshape(heads, self.value_size, self.kv_rank))
         self.out_weight = runtime.matrix(tensors["o_proj.weight"])
+        self.fast = self._row_on_tensor_cores(self.row, runtime.dtype)
+
+    def launch_key(self, ctx: StepContext, page_size: int) -> tuple:
+        """As for the attention mixer: the decode kernel's shape follows the batch and the longest context."""
+        singles = int(ctx.single_tokens.shape[0])
+        if not (self.fast and ops.has_tcgen05_attention(self.row, page_size)) or not singles:
+            return ()
+        return ops.decode_plan(singles, self.num_heads, 1, self.row, page_size, ctx.max_context_len)
+
+    def launch_group(self):
+        return ("latent_attention", self.num_heads, self.row, self.fast)
 
     def cache_need(self):
         # the values are the first kv_rank elements of the rows: no value cache of its own
@@ -96,11 +118,27 @@ class LatentAttention(Mixer):
         q_full = torch.empty((tokens, heads, self.row), dtype=dtype, device=device)
         ops.latent_q_store(q, ctx.positions, self.position.inv_freq, interleaved, q_plain, q_full)
         ops.per_head_project(q_plain, self.k_up_t, q_full[:, :, : self.kv_rank])
-        mixed_latent = torch.empty((tokens, heads, self.kv_rank), dtype=dtype, device=device)
-        ops.paged_attention_generic(
-            q_full, cache.k, None, ctx.block_tables[cache.group], ctx.seq_of_token, ctx.positions, mixed_latent,
-            self.scale, None, ctx.status, values_in_keys=self.kv_rank,
-        )
+        table = ctx.block_tables[cache.group]
+        if self.fast and ops.has_tcgen05_attention(self.row, cache.k.shape[2]):
+            # the cached rows are keys and values at once; the value up-projection reads the first kv_rank
+            mixed_rows = torch.empty((tokens, heads, self.row), dtype=dtype, device=device)
+            if ctx.single_tokens.shape[0]:
+                ops.paged_decode_attention_auto(
+                    q_full, cache.k, cache.k, table, ctx.seq_of_token, ctx.positions, mixed_rows, self.scale, None,
+                    ctx.status, None if ctx.decode_only else ctx.single_tokens, max_context=ctx.max_context_len,
+                )
+            if ctx.q_tiles.shape[0]:
+                ops.paged_prefill_attention(
+                    q_full, cache.k, cache.k, table, ctx.q_tiles, mixed_rows, self.scale, None, ctx.status,
+                    cached_before=ctx.max_portion_start,
+                )
+            mixed_latent = mixed_rows[:, :, : self.kv_rank]
+        else:
+            mixed_latent = torch.empty((tokens, heads, self.kv_rank), dtype=dtype, device=device)
+            ops.paged_attention_generic(
+                q_full, cache.k, None, table, ctx.seq_of_token, ctx.positions, mixed_latent,
+                self.scale, None, ctx.status, values_in_keys=self.kv_rank,
+            )
         mixed = torch.empty((tokens, heads, self.value_size), dtype=dtype, device=device)
         ops.per_head_project(mixed_latent, self.v_up, mixed)
         return ops.project(mixed.view(tokens, -1), self.out_weight, ctx.status)

@@ -77,11 +77,11 @@ class RoutedMLP(FeedForward):
         sorted_x = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
         offsets = ops.moe_dispatch(x, expert_ids, weights, experts, self.weight_on_input, work, place, sorted_x)
         gate_up = torch.empty((rows, 2 * self.intermediate_size), dtype=dtype, device=device)
-        ops.moe_gemm(sorted_x, self.gate_up_weight, offsets, gate_up)
+        ops.moe_gemm(sorted_x, self.gate_up_weight, offsets, gate_up, ctx.status)
         hidden = torch.empty((rows, self.intermediate_size), dtype=dtype, device=device)
         ops.silu_mul(gate_up, hidden)
         y = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
-        ops.moe_gemm(hidden, self.down_weight, offsets, y)
+        ops.moe_gemm(hidden, self.down_weight, offsets, y, ctx.status)
         out = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=device)
         ops.moe_combine(y, expert_ids, place, weights, not self.weight_on_input, add, out, experts)
         return out

@@ -247,7 +247,7 @@ def moe_dispatch(x, expert_ids, weights, num_experts, scale_rows, work, place, s
     return work[2 * num_experts:]
 
 
-def moe_gemm(x, weight, offsets, out):
+def moe_gemm(x, weight, offsets, out, status=None):
     for e in range(weight.shape[0]):
         lo, hi = int(offsets[e]), int(offsets[e + 1])
         if hi > lo:

@@ -174,7 +174,7 @@ def test_router_topk(dev, experts, top, score, renormalise):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens, hidden, inter, experts, top, on_input", [
     (1, 32, 24, 6, 2, True), (50, 48, 40, 4, 2, True), (300, 64, 96, 8, 1, False), (17, 40, 16, 1, 1, True),
-    (64, 128, 72, 16, 4, False), (9, 256, 130, 3, 3, True),
+    (64, 128, 72, 16, 4, False), (9, 256, 130, 3, 3, True), (700, 192, 200, 5, 2, True), (2100, 64, 64, 2, 1, True),
 ])
 def test_routed_feed_forward_steps(dev, dtype, tokens, hidden, inter, experts, top, on_input):
     """Dispatch, the two routed products and the combine, against their plain statements; rows of an
@@ -189,6 +189,7 @@ def test_routed_feed_forward_steps(dev, dtype, tokens, hidden, inter, experts, t
     w2 = (torch.randn((experts, hidden, inter), generator=gen) * inter ** -0.5).to(dtype).to(dev)
     addend = torch.randn((3, tokens, hidden), generator=gen).to(dev)
     outs = []
+    st = status(dev)                   # with it, bfloat16 products take the tcgen05 kernel
     for module in (ops, ref):
         work = torch.zeros(3 * experts + 1, dtype=torch.int32, device=dev)
         place = torch.zeros((tokens, top), dtype=torch.int32, device=dev)
@@ -199,15 +200,15 @@ def test_routed_feed_forward_steps(dev, dtype, tokens, hidden, inter, experts, t
         assert torch.equal(torch.sort(flat_place).values, torch.arange(tokens * top, device=dev))
         assert bool(((flat_place >= offsets[flat_ids]) & (flat_place < offsets[flat_ids + 1])).all())
         gate_up = torch.zeros((tokens * top, 2 * inter), dtype=dtype, device=dev)
-        module.moe_gemm(sorted_x, w1, offsets, gate_up)
+        module.moe_gemm(sorted_x, w1, offsets, gate_up, st)
         hidden_rows = torch.zeros((tokens * top, inter), dtype=dtype, device=dev)
         module.silu_mul(gate_up, hidden_rows)
         y = torch.zeros((tokens * top, hidden), dtype=dtype, device=dev)
-        module.moe_gemm(hidden_rows, w2, offsets, y)
+        module.moe_gemm(hidden_rows, w2, offsets, y, st)
         out = torch.zeros((tokens, hidden), dtype=torch.float32, device=dev)
         module.moe_combine(y, ids, place, weights, not on_input, addend, out, experts)
         outs.append((sorted_x[flat_place], gate_up[flat_place], y[flat_place], out, offsets.clone()))
-    assert torch.equal(outs[0][4], outs[1][4])
+    assert torch.equal(outs[0][4], outs[1][4]) and int(st) == 0
     for got, want in zip(outs[0][:4], outs[1][:4]):
         close(got, want, got.dtype if got.dtype == torch.bfloat16 else (torch.float32 if dtype == torch.float32 else torch.bfloat16))
 
