@@ -118,6 +118,11 @@ def model_numbers(cfg: dict) -> dict:
                 head_flops_per_row=2 * vocab * h)
 
 
+def _tables(manager, name: str) -> list:
+    """A request's block table in every page group of the model."""
+    return [manager.block_table(name, group) for group in range(manager.num_groups)]
+
+
 def decode_requests(batch: int, context: int, runner, manager, tag: str):
     """Requests that stand at position `context`: their pages are reserved, their
     cache holds whatever the pool holds (timing does not depend on the values)."""
@@ -131,7 +136,7 @@ def decode_requests(batch: int, context: int, runner, manager, tag: str):
             raise RuntimeError("the pool is too small for the benchmark")
         requests.append(SimpleNamespace(
             request_id=name, input_token_ids=[int(torch.randint(3, 150000, (1,), generator=generator))],
-            start_position=context, block_tables=[manager.block_table(name, 0)], state_slot=manager.state_slot(name),
+            start_position=context, block_tables=_tables(manager, name), state_slot=manager.state_slot(name),
             need_sample=True))
     return requests
 
@@ -164,7 +169,7 @@ def time_decode(runner, sampler, manager, batch: int, context: int, steps: int, 
             request.start_position += 1
             if request.start_position % PAGE == 0:
                 manager.reserve(request.request_id, request.start_position, request.start_position + 1)
-                request.block_tables = [manager.block_table(request.request_id, 0)]
+                request.block_tables = _tables(manager, request.request_id)
 
     for _ in range(warmup):
         one_step()
@@ -200,7 +205,7 @@ def time_prefill(runner, sampler, manager, tokens: int, repeats: int = 7) -> dic
         name = f"prefill{attempt}"
         manager.reserve(name, 0, tokens)
         request = SimpleNamespace(request_id=name, input_token_ids=ids, start_position=0,
-                                  block_tables=[manager.block_table(name, 0)], state_slot=manager.state_slot(name),
+                                  block_tables=_tables(manager, name), state_slot=manager.state_slot(name),
                                   need_sample=True)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -665,6 +670,235 @@ def tepavik_kernels(peak: dict) -> dict:
     return out
 
 
+def bomipel_sizes(width: int, heads: int, kv_heads: int, size: int, ff: int, experts: int, top: int, kv_rank: int,
+                  rot_dim: int, q_rank: int, layers: int, vocab: int, window: int, keep_first: int) -> dict:
+    """A Bomipel configuration at the layer sizes of a Qwen2 model: latent attention and windowed
+    attention (first positions kept, values mixed) in turn, every layer with a routed feed-forward
+    whose `top` chosen experts together are as wide as the dense feed-forward."""
+    windowed = {"type": "attention", "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": size, "vdim": size, "scale": size ** -0.5, "v_mix": True,
+        "mask": {"size": window, "keep_first": keep_first},
+        "rot": {"base": 500000.0, "dims": size, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": heads, "dim": size, "rot_dim": rot_dim, "vdim": size, "kv_rank": kv_rank, "q_rank": q_rank,
+        "scale": (size + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}}
+    out = []
+    for index in range(layers):
+        layer = dict((latent, windowed)[index % 2])
+        layer["mlp"] = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top}}
+        out.append(layer)
+    return {"architecture": "Bomipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": out}
+
+
+def run_bomipel(args) -> dict:
+    """Prefill and decode throughput of the Bomipel design at the layer sizes of the 0.5B and 1.5B
+    models (random weights, eight layers unless --layers says otherwise: latent attention and
+    windowed attention in turn, eight experts of which two are chosen, together as wide as the dense
+    feed-forward), beside Qwen2 at the same width, heads, layers and vocabulary; then the design's
+    own kernels alone, each beside the kernel of the Qwen2 path that does the like job."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    layers = args.layers or 8
+    result = {"scenario": "bomipel", "layers": layers, "context": CONTEXT, "window": 1024, "keep_first": 4,
+              "experts": 8, "top": 2}
+    # name: width, dense ff, heads, kv heads, head size, latent rank, rotated part, query rank
+    shapes = {"0.5b": (896, 4864, 14, 2, 64, 96, 32, 384), "1.5b": (1536, 8960, 12, 2, 128, 512, 64, 768)}
+    for name, (width, ff, heads, kv_heads, size, kv_rank, rot_dim, q_rank) in shapes.items():
+        qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=True)
+        vocab = qwen["vocab_size"]
+        ours = bomipel_sizes(width, heads, kv_heads, size, ff, 8, 2, kv_rank, rot_dim, q_rank, layers, vocab, 1024, 4)
+        for arch, cfg in (("bomipel", ours), ("qwen2", qwen)):
+            pages = 64 * (CONTEXT // PAGE + 2) + 64
+            runner = ModelRunner.from_random(
+                config_from_dict(cfg), 0,
+                EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=8192,
+                             max_prefill_chunk_len=8192, max_requests=64))
+            manager = CacheManager(runner.group_specs(), runner.num_state_slots)
+            sampler = Sampler(runner.runtime.device, 64)
+            # a latent row beyond 128 elements runs the general attention kernel: the long prompt is left out there
+            prompts = (2048, 8192) if arch == "qwen2" or kv_rank + rot_dim <= 128 else (2048,)
+            for tokens in prompts:
+                timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
+                result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
+                result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
+            for batch in (1, 8, 64):
+                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup)
+                result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
+                result[f"{name}_{arch}_decode_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
+                result[f"{name}_{arch}_decode_b{batch}_launches_per_step"] = timed["launches"] // max(1, args.steps)
+            del runner, manager, sampler
+            torch.cuda.empty_cache()
+    result["kernels"] = bomipel_kernels(peak)
+    return result
+
+
+def bomipel_kernels(peak: dict) -> dict:
+    """The design's kernels alone (microseconds per launch in a CUDA graph of launches on rotating
+    buffers larger than the L2) with the bytes or flops each must move, beside the like kernel of
+    the Qwen2 path: the routed products beside the dense product of as many flops, attention over a
+    window that keeps first positions and over latent rows beside plain causal attention."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out: dict = {}
+    gbs, tflops = peak["hbm_gbs"], peak["bf16_tflops"]
+    turn = [0]
+
+    def rate(key, us, nbytes=0, flops=0):
+        out[key + "_us"] = round(us, 1)
+        if nbytes:
+            out[key + "_hbm_frac"] = round(nbytes / us / 1e3 / gbs, 3)
+        if flops:
+            out[key + "_flops_frac"] = round(flops / us / 1e6 / tflops, 4)
+
+    ops.ensure_built(["routed", "pointwise", "gemm_tcgen05", "attention_generic", "latent"])
+    experts, top = 8, 2
+    for name, width, ff in (("0.5b", 896, 4864), ("1.5b", 1536, 8960)):
+        inter = ff // top
+        copies = 6        # rotating weights: 6 x 8 experts x 3 matrices is beyond the L2
+        w1 = [torch.randn(experts, 2 * inter, width, device=device).bfloat16() * 0.02 for _ in range(copies)]
+        w2 = [torch.randn(experts, width, inter, device=device).bfloat16() * 0.02 for _ in range(copies)]
+        dense1 = [torch.randn(2 * ff, width, device=device).bfloat16() * 0.02 for _ in range(copies)]
+        for tokens in (8, 64, 2048):
+            rows = tokens * top
+            x = torch.randn(tokens, width, device=device).bfloat16()
+            logits = torch.randn(tokens, experts, device=device)
+            ids = torch.empty(tokens, top, dtype=torch.int32, device=device)
+            weights = torch.empty(tokens, top, device=device)
+            work = torch.empty(3 * experts + 1, dtype=torch.int32, device=device)
+            place = torch.empty(tokens, top, dtype=torch.int32, device=device)
+            sorted_x = torch.empty(rows, width, device=device).bfloat16()
+            gate_up = torch.empty(rows, 2 * inter, device=device).bfloat16()
+            hidden = torch.empty(rows, inter, device=device).bfloat16()
+            y = torch.empty(rows, width, device=device).bfloat16()
+            total = torch.empty(tokens, width, device=device)
+            ops.router_topk(logits, top, "sigmoid", False, ids, weights)
+            offsets = ops.moe_dispatch(x, ids, weights, experts, True, work, place, sorted_x)
+
+            def route():
+                ops.router_topk(logits, top, "sigmoid", False, ids, weights)
+                ops.moe_dispatch(x, ids, weights, experts, True, work, place, sorted_x)
+
+            def first():
+                turn[0] += 1
+                ops.moe_gemm(sorted_x, w1[turn[0] % copies], offsets, gate_up, status)
+
+            def second():
+                turn[0] += 1
+                ops.moe_gemm(hidden, w2[turn[0] % copies], offsets, y, status)
+
+            def dense():
+                turn[0] += 1
+                ops.project(x, dense1[turn[0] % copies], status)
+
+            key = f"{name}_t{tokens}"
+            touched = min(experts, rows)                     # experts whose weights a step reads
+            flops1, flops2 = 2 * rows * 2 * inter * width, 2 * rows * width * inter
+            rate(key + "_routed_gate_up", _graph_time_us(first, copies), nbytes=touched * 2 * inter * width * 2, flops=flops1)
+            rate(key + "_routed_down", _graph_time_us(second, copies), nbytes=touched * inter * width * 2, flops=flops2)
+            rate(key + "_dense_gate_up", _graph_time_us(dense, copies), nbytes=2 * ff * width * 2, flops=2 * tokens * 2 * ff * width)
+            rate(key + "_route_and_dispatch", _graph_time_us(route, 4), nbytes=(tokens + 2 * rows) * width * 2)
+            rate(key + "_combine", _graph_time_us(
+                lambda: ops.moe_combine(y, ids, place, weights, False, None, total, experts), 4),
+                nbytes=rows * width * 2 + tokens * width * 4)
+        del w1, w2, dense1
+    # --- attention: 2,048-token prompt and 64 decoding requests at 4,096 tokens
+    for heads, kv_heads, size, rank, rot in ((14, 2, 64, 96, 32), (12, 2, 128, 512, 64)):
+        tag = f"h{heads}_d{size}"
+        window, keep = 1024, 4
+        libraries = list(ops.attention_libraries(size, PAGE))
+        if rank + rot in (64, 128):
+            libraries += list(ops.attention_libraries(rank + rot, PAGE))
+        ops.ensure_built(libraries)
+        tokens = 2048
+        pages = tokens // PAGE
+        tiles = torch.tensor([[0, first, 128, first] for first in range(0, tokens, 128)], dtype=torch.int32, device=device)
+        seq0 = torch.zeros(tokens, dtype=torch.int32, device=device)
+        pos0 = torch.arange(tokens, dtype=torch.int32, device=device)
+        table = torch.arange(pages, dtype=torch.int32, device=device).view(1, -1)
+        k = torch.randn(pages + 2, kv_heads, PAGE, size, device=device).bfloat16()
+        v = torch.randn_like(k)
+        q = torch.randn(tokens, heads, size, device=device).bfloat16()
+        o = torch.empty_like(q)
+        window_flops = 4 * heads * size * (tokens * window - window * window / 2)
+        rate(tag + "_prefill_window_tensor_cores", _graph_time_us(
+            lambda: ops.paged_prefill_attention(q, k, v, table, tiles, o, size ** -0.5, window, status, cached_before=0), 4),
+            flops=window_flops)
+        rate(tag + "_prefill_window_keep_first", _graph_time_us(
+            lambda: ops.windowed_attention(q, k, v, table, seq0, pos0, tiles, None, o, size ** -0.5, window, keep, status,
+                                           max_context=tokens, cached_before=0), 4), flops=window_flops)
+        rate(tag + "_prefill_causal_tensor_cores", _graph_time_us(
+            lambda: ops.paged_prefill_attention(q, k, v, table, tiles, o, size ** -0.5, None, status, cached_before=0), 4),
+            flops=4 * heads * size * tokens * tokens / 2)
+        row = rank + rot
+        kl = torch.randn(pages + 2, 1, PAGE, row, device=device).bfloat16()
+        ql = torch.randn(tokens, heads, row, device=device).bfloat16()
+        latent_flops = 2 * heads * (row + rank) * tokens * tokens / 2
+        if row in (64, 128):
+            ol = torch.empty_like(ql)
+            rate(tag + f"_prefill_latent_row{row}_tensor_cores", _graph_time_us(
+                lambda: ops.paged_prefill_attention(ql, kl, kl, table, tiles, ol, row ** -0.5, None, status, cached_before=0), 4),
+                flops=latent_flops)
+        ol = torch.empty(tokens, heads, rank, device=device).bfloat16()
+        rate(tag + f"_prefill_latent_row{row}_general", _graph_time_us(
+            lambda: ops.paged_attention_generic(ql, kl, None, table, seq0, pos0, ol, row ** -0.5, None, status,
+                                                values_in_keys=rank), 2), flops=latent_flops)
+        batch, context = 64, CONTEXT
+        pages = context // PAGE
+        launches = 4
+        seq = torch.arange(batch, dtype=torch.int32, device=device)
+        positions = torch.full((batch,), context - 1, dtype=torch.int32, device=device)
+        tables = [torch.arange(i * pages * batch, (i + 1) * pages * batch, dtype=torch.int32, device=device).view(batch, pages)
+                  for i in range(launches)]
+        k = torch.randn(pages * batch * launches + 2, kv_heads, PAGE, size, device=device).bfloat16()
+        v = torch.randn_like(k)
+        qd = torch.randn(batch, heads, size, device=device).bfloat16()
+        od = torch.empty_like(qd)
+
+        def windowed_decode(kept):
+            turn[0] += 1
+            ops.windowed_attention(qd, k, v, tables[turn[0] % launches], seq, positions, None, None, od, size ** -0.5,
+                                   window, kept, status, max_context=context, cached_before=0)
+
+        window_bytes = 2 * batch * (window + keep) * kv_heads * size * 2
+        rate(tag + "_decode_b64_window_tensor_cores", _graph_time_us(lambda: windowed_decode(0), launches), nbytes=window_bytes)
+        rate(tag + "_decode_b64_window_keep_first", _graph_time_us(lambda: windowed_decode(keep), launches), nbytes=window_bytes)
+        del k, v
+        kl = torch.randn(pages * batch * launches + 2, 1, PAGE, row, device=device).bfloat16()
+        ql = torch.randn(batch, heads, row, device=device).bfloat16()
+        latent_bytes = batch * context * row * 2
+        if row in (64, 128):
+            ol = torch.empty_like(ql)
+
+            def latent_decode():
+                turn[0] += 1
+                ops.paged_decode_attention_auto(ql, kl, kl, tables[turn[0] % launches], seq, positions, ol, row ** -0.5, None,
+                                                status, max_context=context)
+
+            rate(tag + f"_decode_b64_latent_row{row}_tensor_cores", _graph_time_us(latent_decode, launches), nbytes=latent_bytes)
+        ol = torch.empty(batch, heads, rank, device=device).bfloat16()
+
+        def latent_general():
+            turn[0] += 1
+            ops.paged_attention_generic(ql, kl, None, tables[turn[0] % launches], seq, positions, ol, row ** -0.5, None,
+                                        status, values_in_keys=rank)
+
+        rate(tag + f"_decode_b64_latent_row{row}_general", _graph_time_us(latent_general, launches), nbytes=latent_bytes)
+        del kl
+    out["status"] = int(status)
+    return out
+
+
 def run_decode_sizes(args) -> dict:
     """Decode at the 1.5B and 7B sizes of the family (batch 8 and 64, context 4,096) with the
     fraction of the HBM roofline each step reaches: at these sizes a step's kernels are long
@@ -1001,7 +1235,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -1037,7 +1271,7 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik,
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik, "bomipel": run_bomipel,
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)

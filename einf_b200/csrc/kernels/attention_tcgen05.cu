@@ -362,6 +362,7 @@ struct TcAttentionParams {
   __nv_bfloat16* out;       // [tokens, heads, D]
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
+  int keep_first;           // with a window: the first that many positions of the sequence stay visible (0: none)
   int chunk;                // chunked mask: a row sees only the keys of its own block of this many positions (0: off)
   float scale, softcap;     // scores are multiplied by scale; with a cap z they become z * tanh(score / z)
 };
@@ -415,9 +416,19 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     k_begin = min(k_end, k_begin + (int)rank * per);
     k_end = min(k_end, k_begin + per);
   }
-  const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  // A window that keeps the first positions of the sequence: the kept keys that lie before the
+  // window's own tiles come first, as tiles of their own (keys 0 .. kept_end - 1; a kept key inside
+  // the window's tiles is seen there).  The CTAs of a cluster would all have to take them: such a
+  // launch runs without clusters.
+  const int kept_end = (p.window > 0 && p.keep_first > 0 && csize == 1) ? min(p.keep_first, k_begin) : 0;
+  const int kept_tiles = (kept_end + kBlockKV - 1) / kBlockKV;
+  const int main_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  const int num_tiles = kept_tiles + main_tiles;
   const int pages_per_tile = kBlockKV / p.page_size;
   const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
+  // first key of tile i, and one past the last key it holds
+  auto tile_key0 = [&](int i) { return i < kept_tiles ? i * kBlockKV : k_begin + (i - kept_tiles) * kBlockKV; };
+  auto tile_key_end = [&](int i) { return i < kept_tiles ? min(kept_end, (i + 1) * kBlockKV) : min(k_end, tile_key0(i) + kBlockKV); };
 
   if (threadIdx.x == 0) {
     bar_init(q_full, 1);
@@ -461,14 +472,12 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     const CUtensorMap* map = which ? &map_v : &map_k;
     const CUtensorMap* run_map = which ? &run_v : &run_k;
     const int page_shift = __ffs(p.page_size) - 1;            // a page is a power of two tokens
-    const int first_entry = k_begin >> page_shift;
-    const int tail_pages = num_tiles > 0 ? (k_end - (k_begin + (num_tiles - 1) * kBlockKV) + p.page_size - 1) >> page_shift : 0;
-    auto pages_of = [&](int i) { return i + 1 < num_tiles ? pages_per_tile : tail_pages; };
+    auto pages_of = [&](int i) { return (tile_key_end(i) - tile_key0(i) + p.page_size - 1) >> page_shift; };
     // Lane g's page of tile i, read two tiles before its use: the block table's latency would
     // otherwise stand between a freed stage and its next load.
     auto read_page = [&](int i) {
       if (i >= num_tiles || lane >= pages_of(i)) return 0;
-      return table[first_entry + i * pages_per_tile + lane];   // one coalesced read per tile
+      return table[(tile_key0(i) >> page_shift) + lane];   // one coalesced read per tile
     };
     bool bad = false;
     int page = read_page(0), page_next = read_page(1);
@@ -612,7 +621,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       m_ref = m_to;
     };
     for (int i = g; i < num_tiles && ok; i += 2, ++done) {
-      const int key0 = k_begin + i * kBlockKV;
+      const int key0 = tile_key0(i);
       // A P buffer is free once the second product of the tile that used it is complete, and the
       // accumulator may be rescaled once the second product of this warpgroup's previous tile is.
       // That one started when the previous tile's P was written, a moment ago: the wait for it comes
@@ -642,18 +651,23 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
       // A tile that lies wholly before this row's position (and inside its window) needs no mask;
       // in a tile on the diagonal or at a window's edge, column c of the tile is set to -inf
       // (probability 2^-inf = 0) unless c_lo <= c <= c_hi, before anything else looks at it.
-      const int c_hi = pos - key0, c_lo = pos_lo - key0;
-      const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && c_lo <= 0);
+      // With kept first positions column c is also visible where c < c_keep (and c <= c_hi): in a
+      // tile of kept keys that is all there is (its c_lo lies beyond the tile).
+      const bool kept_tile = i < kept_tiles;
+      const int c_hi = pos - key0, c_lo = kept_tile ? 2 * kBlockKV : pos_lo - key0;
+      const int c_keep = p.keep_first > 0 && p.window > 0 ? (kept_tile ? kept_end : p.keep_first) - key0 : 0;
+      const bool warp_all_visible = __all_sync(0xffffffffu, c_hi >= kBlockKV - 1 && (c_lo <= 0 || c_keep >= kBlockKV));
       auto mask = [&](float* sv, int c0) {
-        const int hi = c_hi - c0, lo = c_lo - c0;
+        const int hi = c_hi - c0, lo = c_lo - c0, keep = c_keep - c0;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && c >= lo) ? sv[c] : -INFINITY;
+        for (int c = 0; c < 32; ++c) sv[c] = (c <= hi && (c >= lo || c < keep)) ? sv[c] : -INFINITY;
       };
       const uint32_t s_row = s_tile + lane_addr;
       unsigned char* p_row = gbase + kPOff + (g * kPBuffers + done % kPBuffers) * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
       // A row without a reference that sees a key in this tile (its first tile; with a window, the
       // first that reaches into it) gets one from a walk for the maximum before anything else.
-      bool walked = __any_sync(0xffffffffu, m_ref == -INFINITY && c_hi >= 0 && c_lo < kBlockKV && c_lo <= c_hi);
+      bool walked = __any_sync(0xffffffffu, m_ref == -INFINITY && c_hi >= 0 &&
+                                            ((c_lo < kBlockKV && c_lo <= c_hi) || c_keep > 0));
       float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll 1
       for (int attempt = 0; attempt < 2; ++attempt) {
@@ -966,6 +980,7 @@ struct TcDecodeParams {
   __nv_bfloat16* out;       // [tokens, heads, D]
   int* status;
   int num_heads, num_kv_heads, page_size, num_pages, table_width, window;
+  int keep_first;           // see TcAttentionParams
   int chunk;                // see TcAttentionParams
   float scale, softcap;
   // A token's keys split over `splits` clusters, which meet in global memory: every cluster writes its
@@ -1048,7 +1063,14 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
   per = (per + kBlockKV - 1) / kBlockKV * kBlockKV;
   const int k_begin = min(pos + 1, lo_page + (split * (int)csize + (int)rank) * per);
   const int k_end = min(pos + 1, k_begin + per);
-  const int num_tiles = (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  // A window that keeps the first positions of the sequence: the kept keys before the window's
+  // own tiles (0 .. kept_end - 1) are tiles of their own, ahead of the others, in the token's first CTA.
+  const int keep_first = p.window > 0 ? p.keep_first : 0;
+  const int kept_end = (keep_first > 0 && split == 0 && rank == 0) ? min(keep_first, lo_page) : 0;
+  const int kept_tiles = (kept_end + kBlockKV - 1) / kBlockKV;
+  const int num_tiles = kept_tiles + (k_end - k_begin + kBlockKV - 1) / kBlockKV;
+  auto tile_key0 = [&](int i) { return i < kept_tiles ? i * kBlockKV : k_begin + (i - kept_tiles) * kBlockKV; };
+  auto tile_key_end = [&](int i) { return i < kept_tiles ? min(kept_end, (i + 1) * kBlockKV) : k_end; };
   const int* table = p.block_table + (size_t)p.seq_of_token[t] * p.table_width;
   const int pages_per_tile = kBlockKV / p.page_size;
   const uint32_t page_bytes = (uint32_t)p.page_size * 128u;   // one page of one 64-wide slice
@@ -1076,11 +1098,11 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     // global memory does not sit between a freed stage and its next load.
     bool bad = false;
     auto pages_of = [&](int i) {
-      const int key0 = k_begin + i * kBlockKV;
-      return min(pages_per_tile, (k_end - key0 + p.page_size - 1) / p.page_size);
+      const int key0 = tile_key0(i);
+      return min(pages_per_tile, (tile_key_end(i) - key0 + p.page_size - 1) / p.page_size);
     };
     auto page_of = [&](int i) {
-      return (i < num_tiles && lane < pages_of(i)) ? table[(k_begin + i * kBlockKV) / p.page_size + lane] : 0;
+      return (i < num_tiles && lane < pages_of(i)) ? table[tile_key0(i) / p.page_size + lane] : 0;
     };
     int next_page = page_of(0);
     for (int i = 0; i < num_tiles; ++i) {
@@ -1102,7 +1124,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       // and value) and before the first bounded wait that only progress of this kernel's other
       // warps, which need the query, can end: a bounded wait must not run while the wait for
       // another kernel is still open.
-      if (i >= kDecStages || k_begin + (i + 1) * kBlockKV > pos) pdl_wait();
+      if (i >= kDecStages || tile_key0(i) + kBlockKV > pos) pdl_wait();
       int ok = 1;
       if (i >= kDecStages && lane == 0) ok = bar_wait(kv_empty(s), ((i / kDecStages) & 1) ^ 1, p.status) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -1228,8 +1250,8 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     // nothing is waited for any more and the results are garbage, but the walk goes on to its end.
     const ScoreScale sc = make_score_scale(p.scale, p.softcap);
     for (int i = 0; i < num_tiles; ++i) {
-      const int j = k_begin + i * kBlockKV + r;                  // this thread's key
-      const bool visible = j >= lo && j < k_end;
+      const int j = tile_key0(i) + r;                            // this thread's key
+      const bool visible = i < kept_tiles ? j < kept_end : ((j >= lo || j < keep_first) && j < k_end);
       ok = ok && bar_wait_likely_done(s_full(i & 1), (i >> 1) & 1, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sv[16];
@@ -1500,10 +1522,11 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
                                                     const int* block_table, const int* tiles, int num_tiles,
                                                     void* out, int num_tokens, int num_heads, int num_kv_heads,
                                                     int page_size, int num_pages, int table_width, float scale,
-                                                    int window, int chunk, float softcap, int cluster, int* status,
-                                                    cudaStream_t stream) {
+                                                    int window, int keep_first, int chunk, float softcap, int cluster,
+                                                    int* status, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (cluster < 1 || cluster > 8) return (int)cudaErrorInvalidValue;
+  if (keep_first < 0 || (keep_first > 0 && window > 0 && cluster != 1)) return (int)cudaErrorInvalidValue;
   if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
   CUtensorMap map_q, map_k, map_v;
   int rc = make_map(&map_q, q, num_tokens, (long long)num_heads * D, kBlockQ);
@@ -1529,6 +1552,7 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   p.num_pages = num_pages;
   p.table_width = table_width;
   p.window = window;
+  p.keep_first = keep_first;
   p.chunk = chunk;
   p.scale = scale;
   p.softcap = softcap;
@@ -1598,7 +1622,7 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
                                                    const int* positions, const int* token_list, void* out,
                                                    int num_tokens, int num_heads, int num_kv_heads, int page_size,
                                                    int num_pages, int table_width, float scale, int window,
-                                                   int chunk, float softcap, int cluster, int splits,
+                                                   int keep_first, int chunk, float softcap, int cluster, int splits,
                                                    float* split_out, int* split_count, int* status,
                                                    cudaStream_t stream) {
   if (num_tokens == 0) return 0;
@@ -1630,6 +1654,7 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   p.num_pages = num_pages;
   p.table_width = table_width;
   p.window = window;
+  p.keep_first = keep_first < 0 ? 0 : keep_first;
   p.chunk = chunk;
   p.scale = scale;
   p.softcap = softcap;

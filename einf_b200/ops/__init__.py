@@ -1329,6 +1329,48 @@ def _plan_decode(num_tokens: int, num_heads: int, num_kv_heads: int, head_size: 
     return "tcgen05", best[0], best[1]
 
 
+def windowed_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    q_tiles: Optional[torch.Tensor],
+    single_tokens: Optional[torch.Tensor],
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    keep_first: int,
+    status: torch.Tensor,
+    max_context: Optional[int] = None,
+    cached_before: Optional[int] = None,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
+) -> None:
+    """Attention of a whole step with any of the masks (window, first positions kept, chunks) and a soft
+    cap: bfloat16 heads of 64 or 128 with values as large as keys run the tcgen05 kernels, the single
+    tokens (``single_tokens``: their packed indices, None when the step has nothing else) by the
+    decode kernel and the 128-row tiles of prompt portions (``q_tiles``) by the prefill kernel, side by
+    side; everything else the general kernel.  The kept positions widen what a token reads by
+    ``keep_first`` keys at most, so the decode kernel's shape is planned for window + keep_first."""
+    head_size, page_size = q.shape[2], k_cache.shape[2]
+    if (q.dtype == torch.bfloat16 and v_cache is not None and v_cache.shape == k_cache.shape
+            and has_tcgen05_attention(head_size, page_size)):
+        tiles = q_tiles is not None and q_tiles.shape[0] > 0
+        decode = single_tokens.shape[0] > 0 if single_tokens is not None else not tiles
+        if decode:
+            paged_decode_attention_auto(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
+                                        status, single_tokens, max_context=max_context, chunk=chunk, softcap=softcap,
+                                        keep_first=keep_first)
+        if q_tiles is not None and q_tiles.shape[0]:
+            paged_prefill_attention(q, k_cache, v_cache, block_table, q_tiles, out, scale, window, status,
+                                    cached_before=cached_before, chunk=chunk, softcap=softcap, keep_first=keep_first)
+        return
+    paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status,
+                            chunk=chunk, softcap=softcap, keep_first=keep_first)
+
+
 def paged_decode_attention_auto(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -1344,6 +1386,7 @@ def paged_decode_attention_auto(
     max_context: Optional[int] = None,
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
+    keep_first: int = 0,
 ) -> None:
     """Decode attention by the kernel, cluster size and number of clusters per token that
     ``decode_plan`` picks for this batch; ``max_context`` is the longest context among the
@@ -1356,9 +1399,11 @@ def paged_decode_attention_auto(
     kernel, cluster, splits = decode_plan(tokens, q.shape[1], k_cache.shape[1], q.shape[2], k_cache.shape[2], max_context)
     if kernel == "tcgen05":
         paged_decode_attention_tcgen05(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
-                                       cluster, status, token_list, splits, chunk=chunk, softcap=softcap)
-    elif chunk or softcap:
-        raise UnsupportedSize("a chunked mask or a soft cap needs the tcgen05 decode kernel (head size 64 or 128)")
+                                       cluster, status, token_list, splits, chunk=chunk, softcap=softcap,
+                                       keep_first=keep_first)
+    elif chunk or softcap or (window and keep_first):
+        raise UnsupportedSize("a chunked mask, a soft cap or kept first positions need the tcgen05 decode kernel "
+                              "(head size 64 or 128)")
     else:
         paged_decode_attention_cluster(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
                                        cluster, status, token_list)
@@ -1444,6 +1489,7 @@ def paged_decode_attention_tcgen05(
     splits: int = 1,
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
+    keep_first: int = 0,
 ) -> None:
     """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
     (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
@@ -1469,7 +1515,7 @@ def paged_decode_attention_tcgen05(
         shares, counters = _decode_split_workspace(tokens * num_kv_heads * head_blocks, splits, q.device)
     fn = _fn(
         "einf_paged_decode_attention_tcgen05",
-        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+        [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
          c_void_p],
         f"HEAD_SIZE={head_size}",
     )
@@ -1479,6 +1525,7 @@ def paged_decode_attention_tcgen05(
            _opt(positions, "positions", torch.int32), _opt(token_list, "token_list", torch.int32), _dev(out, "out"),
            tokens, num_heads, num_kv_heads, page_size,
            num_pages, block_table.shape[1], float(scale), int(window) if window else 0,
+           int(keep_first) if window else 0,
            int(chunk) if chunk else 0, float(softcap) if softcap else 0.0, cluster,
            splits, shares.data_ptr() if splits > 1 else None, counters.data_ptr() if splits > 1 else None,
            _dev(status, "status"), _stream()),
@@ -1542,6 +1589,7 @@ def paged_prefill_attention(
     cached_before: Optional[int] = None,
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
+    keep_first: int = 0,
 ) -> None:
     """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
@@ -1567,7 +1615,7 @@ def paged_prefill_attention(
             )
         fn = _fn(
             "einf_paged_prefill_attention_tcgen05",
-            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_float, c_int, c_void_p,
+            [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                                                  c_void_p],
             f"HEAD_SIZE={head_size}",
         )
@@ -1577,17 +1625,21 @@ def paged_prefill_attention(
                 if cached_before is not None and bound:
                     cached_before = min(cached_before, int(bound))
             cluster = prefill_cluster_size(num_heads * q_tiles.shape[0], head_size, cached_before)
+        if window and keep_first:
+            cluster = 1       # the kept keys are tiles of their own ahead of the window's: one CTA walks both
         _check(
             fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
                _opt(block_table, "block_table", torch.int32), _dev(q_tiles, "q_tiles"), q_tiles.shape[0],
                _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1],
-               float(scale), int(window) if window else 0, int(chunk) if chunk else 0,
+               float(scale), int(window) if window else 0, int(keep_first) if window else 0,
+               int(chunk) if chunk else 0,
                float(softcap) if softcap else 0.0, int(cluster), _dev(status, "status"), _stream()),
             "paged_prefill_attention_tcgen05",
         )
         return
-    if chunk or softcap:
-        raise UnsupportedSize("a chunked mask or a soft cap needs the tcgen05 prefill kernel (head size 64 or 128)")
+    if chunk or softcap or (window and keep_first):
+        raise UnsupportedSize("a chunked mask, a soft cap or kept first positions need the tcgen05 prefill kernel "
+                              "(head size 64 or 128)")
     fn = _fn(
         "einf_paged_prefill_attention",
         [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p],

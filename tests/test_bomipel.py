@@ -92,13 +92,16 @@ CONFIGS = {
         attention(4, 2, 64, 32, size=50, keep_first=17, rot_dims=32, scaling=SCALING, v_mix=True),
         attention(6, 2, 32, 32, size=33, keep_first=2, rot_dims=32, v_mix=True),
     ], [moe(96, 8, 2), moe(64, 4, 1), moe(32, 16, 4)]),
-    # sizes the tensor-core kernels take: latent rows of 128 and 64, a windowed layer with heads of 64
-    # and nothing kept
+    # sizes the tensor-core kernels take: latent rows of 128 and 64, windowed layers with heads of 64,
+    # nothing kept, a few positions kept, more positions kept than the window is wide
     "cores": model(64, 83, [
         latent(4, 32, 32, 32, 96, 48),
         attention(4, 2, 64, 64, size=40, keep_first=0, rot_dims=32),
         latent(2, 16, 16, 24, 48, 32, base=700.0),
-    ], [moe(64, 4, 2), moe(32, 2, 1), None]),
+        attention(2, 1, 64, 64, size=21, keep_first=5, rot_dims=16, v_mix=True),
+        attention(2, 1, 128, 64, size=33, keep_first=3, v_mix=True),
+        attention(3, 1, 64, 64, size=19, keep_first=70, rot_dims=64, v_mix=True),
+    ], [moe(64, 4, 2), moe(32, 2, 1), None, moe(48, 3, 2), None, moe(32, 2, 2)]),
 }
 PAGE = {"mix": 4, "ones": 8, "wide": 16, "cores": 16}
 SINGLE = {

@@ -82,6 +82,41 @@ def test_attention_with_kept_first_positions(dev, dtype, heads, kv_heads, size, 
     assert (out - want).abs().max() > 1e-2
 
 
+@pytest.mark.parametrize("size, page_size", [(64, 16), (128, 16), (64, 8), (128, 64), (64, 128)])
+@pytest.mark.parametrize("window, keep", [(40, 4), (200, 130), (128, 128), (17, 300), (1, 1), (500, 16), (64, 0)])
+def test_tensor_core_attention_with_kept_first_positions(dev, size, page_size, window, keep):
+    """The tcgen05 prefill and decode kernels behind ``windowed_attention``: portions that start at 0,
+    inside the kept positions, inside the first window and far beyond it, and single tokens at
+    every distance, against the plain statement."""
+    from einf_b200 import ops
+
+    heads, kv_heads = 6, 2
+    portions = [(0, 300), (3, 130), (700, 260), (129, 5), (1500, 128)]
+    singles = [(0, 1), (keep, 1), (max(keep - 1, 0), 1), (window + keep, 1), (window + keep + 1, 1), (1000, 1), (2047, 1),
+               (127, 1), (128, 1)]
+    for requests in (portions, singles, portions[:2] + singles[:5]):
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, torch.bfloat16, heads, kv_heads, size, page_size,
+                                                                requests, window)
+        tiles, single_tokens, cursor = [], [], 0
+        for index, (start, count) in enumerate(requests):
+            if count == 1:
+                single_tokens.append(cursor)
+            else:
+                for first in range(0, count, 128):
+                    tiles.append([index, cursor + first, min(128, count - first), start + first])
+            cursor += count
+        q_tiles = torch.tensor(tiles, dtype=torch.int32, device=dev).reshape(-1, 4)
+        token_list = torch.tensor(single_tokens, dtype=torch.int32, device=dev) if tiles else None
+        out = torch.zeros_like(q)
+        want = torch.zeros_like(q)
+        st = status(dev)
+        ops.windowed_attention(q, k, v, table, seq, pos, q_tiles, token_list, out, scale, window, keep, st,
+                               max_context=max(s + c for s, c in requests), cached_before=max(s for s, _ in requests))
+        ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st, keep_first=keep)
+        assert int(st) == 0
+        close(out, want, torch.bfloat16)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, row, rank, page_size", [(3, 32, 24, 4), (16, 80, 64, 16), (5, 576, 512, 16), (1, 10, 8, 8)])
 def test_attention_with_values_in_the_key_rows(dev, dtype, heads, row, rank, page_size):
