@@ -1235,7 +1235,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel", "bomipel-kernels"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -1272,6 +1272,7 @@ def main() -> int:
         print(json.dumps(line))
         return 0
     scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik, "bomipel": run_bomipel,
+                 "bomipel-kernels": lambda args: {"scenario": "bomipel-kernels", "kernels": bomipel_kernels(peaks())},
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
         line = scenarios[args.scenario](args)

@@ -523,11 +523,12 @@ extern "C" int einf_gemm_tcgen05_splits(int k, int splits) {
 }
 
 // The token tile of the grouped product for `rows` rows over `groups` groups: about one and a half
-// times the average rows of a group, a multiple of 16 between 16 and 256.
+// times the average rows of a group, a multiple of 16 between 16 and 128 (at 128 two CTAs share an
+// SM, so that one's epilogue runs beside the other's products).
 extern "C" int einf_gemm_grouped_tcgen05_token_tile(int rows, int groups) {
   const int average = (rows + groups - 1) / (groups > 0 ? groups : 1);
   int tile = (average * 3 / 2 + 15) / 16 * 16;
-  return tile < 16 ? 16 : (tile > 256 ? 256 : tile);
+  return tile < 16 ? 16 : (tile > 128 ? 128 : tile);
 }
 
 // x: [rows, k] bfloat16 contiguous, sorted by group; w: [groups, n, k] bfloat16 contiguous; offsets: [groups + 1]

@@ -8,8 +8,10 @@ names, the cache plan with its windowed groups, batch packing, replay and schedu
 
 A routed feed-forward makes bfloat16 comparisons delicate: where two router logits are closer than
 the rounding of the router's input, either expert may be taken, and everything after that token
-differs.  The plain model reports the router's margins; a bfloat16 comparison of a request stops
-before its first close call (the float32 comparison never does).
+differs; with a few routed layers that happens within a dozen tokens.  So the bfloat16 scenarios run
+a variant of every configuration in which each token takes all experts of a layer (the same weights,
+``top`` = ``experts``: every kernel of the routed path runs, no choice can flip) and compare every
+position; which experts are chosen is float32's to test, and the router kernel's own test.
 """
 from __future__ import annotations
 
@@ -119,6 +121,15 @@ def write_folder(folder, config, weights):
     save_file({k: v.contiguous() for k, v in weights.items()}, str(folder / "model.safetensors"))
 
 
+def all_experts(config):
+    """The same model with every expert of a layer chosen for every token."""
+    config = json.loads(json.dumps(config))
+    for layer in config["layers"]:
+        if layer["mlp"] is not None:
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+    return config
+
+
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     base = tmp_path_factory.mktemp("bomipel")
@@ -127,6 +138,8 @@ def folders(tmp_path_factory):
         weights = bomipel_plain.random_model(config, 20 + index)
         write_folder(base / name, config, weights)
         made[name] = (base / name, config, weights)
+        write_folder(base / (name + "_all"), all_experts(config), weights)
+        made[name + "_all"] = (base / (name + "_all"), all_experts(config), weights)
     return made
 
 
@@ -164,8 +177,9 @@ def check(rows, expected, dtype, close=None):
             continue
         difference = rows[key] - expected[key]
         error = float(np.sqrt(np.mean((difference - difference.mean()) ** 2))) / size
-        assert error < 0.04, f"first wrong token: {key}, error {error:.3f}"
+        assert error < 0.03, f"first wrong token: {key}, error {error:.3f}"
         compared += 1
+    assert compared == len(expected) or close is not None
     return compared
 
 
@@ -460,7 +474,7 @@ def test_a_far_key_decides_the_row_emulated(tmp_path, emulated):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(SINGLE))
 def test_each_mechanism_alone(name, dtype, folders):
-    folder, config, weights = folders[name]
+    folder, config, weights = folders[name if dtype == "float32" else name + "_all"]
     replay_modes(folder, config, weights, 4, dtype, "cuda:0", lengths=(1, 6, 19, 70))
 
 
@@ -468,7 +482,7 @@ def test_each_mechanism_alone(name, dtype, folders):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_replay_modes(name, dtype, folders):
-    folder, config, weights = folders[name]
+    folder, config, weights = folders[name if dtype == "float32" else name + "_all"]
     replay_modes(folder, config, weights, PAGE[name], dtype, "cuda:0", lengths=(1, 5, 9, 23, 37, 50, 131))
 
 
