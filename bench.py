@@ -709,12 +709,15 @@ def run_bomipel(args) -> dict:
     result = {"scenario": "bomipel", "layers": layers, "context": CONTEXT, "window": 1024, "keep_first": 4,
               "experts": 8, "top": 2}
     # name: width, dense ff, heads, kv heads, head size, latent rank, rotated part, query rank
-    shapes = {"0.5b": (896, 4864, 14, 2, 64, 96, 32, 384), "1.5b": (1536, 8960, 12, 2, 128, 512, 64, 768)}
+    shapes = {"0.5b": (896, 4864, 14, 2, 64, 96, 32, 384), "1.5b": (1536, 8960, 12, 2, 128, 96, 32, 768),
+              "1.5b-row576": (1536, 8960, 12, 2, 128, 512, 64, 768)}
     for name, (width, ff, heads, kv_heads, size, kv_rank, rot_dim, q_rank) in shapes.items():
-        qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=True)
+        qwen = dict(SIZES["1.5b"] if name.startswith("1.5b") else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=True)
         vocab = qwen["vocab_size"]
         ours = bomipel_sizes(width, heads, kv_heads, size, ff, 8, 2, kv_rank, rot_dim, q_rank, layers, vocab, 1024, 4)
         for arch, cfg in (("bomipel", ours), ("qwen2", qwen)):
+            if arch == "qwen2" and name == "1.5b-row576":
+                continue          # measured with the other 1.5B shape
             pages = 64 * (CONTEXT // PAGE + 2) + 64
             runner = ModelRunner.from_random(
                 config_from_dict(cfg), 0,
@@ -894,6 +897,14 @@ def bomipel_kernels(peak: dict) -> dict:
                                         status, values_in_keys=rank)
 
         rate(tag + f"_decode_b64_latent_row{row}_general", _graph_time_us(latent_general, launches), nbytes=latent_bytes)
+        shares = ops.latent_decode_splits(batch, heads, context)
+
+        def latent_shared():
+            turn[0] += 1
+            ops.latent_decode_attention(ql, kl, tables[turn[0] % launches], seq, positions, ol, row ** -0.5, shares, status)
+
+        rate(tag + f"_decode_b64_latent_row{row}_shared_rows", _graph_time_us(latent_shared, launches), nbytes=latent_bytes)
+        out[tag + f"_decode_b64_latent_row{row}_shares"] = shares
         del kl
     out["status"] = int(status)
     return out

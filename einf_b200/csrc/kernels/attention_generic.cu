@@ -149,6 +149,194 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode steps over rows that all query heads share (one key/value head whose values are the
+// leading `value_size` elements of its key rows: a latent cache).  The kernel above gives every
+// (token, head) a warp that walks all keys alone and reads each key row once per head; here a CTA
+// takes one token, up to sixteen of its heads and one share of its keys, stages 32 key rows at a
+// time in shared memory (read once from global memory for all sixteen heads, 16 bytes per
+// access), and its eight warps take two heads each: a lane owns one key of the tile for the
+// scores and a stripe of value dimensions for the mixing.  The shares of a token's keys (grid x)
+// leave unnormalised (accumulator, maximum, sum) triples in a workspace, which a second kernel
+// adds up in share order; with one share the CTA writes the result itself.
+// Arithmetic and order of additions are 32-bit and fixed per (token, head): nothing depends on
+// what else the batch holds.
+// ---------------------------------------------------------------------------
+constexpr int kSharedWarps = 8;
+constexpr int kSharedHeads = 2 * kSharedWarps;   // heads a CTA takes
+constexpr int kSharedTile = 32;                  // keys per tile
+
+template <typename T, int kDimsPerLane>
+__global__ void __launch_bounds__(kSharedWarps * 32)
+latent_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                               T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                               int num_heads, int row_size, int value_size, int page_size, int num_pages,
+                               int table_width, float scale, int* status) {
+  extern __shared__ __align__(16) unsigned char shared_raw[];
+  const int row_pad = row_size + 16 / (int)sizeof(T);            // rows 16 bytes apart from a multiple of the banks
+  float* q_s = reinterpret_cast<float*>(shared_raw);              // [kSharedHeads][row_size]
+  T* k_s = reinterpret_cast<T*>(q_s + kSharedHeads * row_size);   // [kSharedTile][row_pad]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.y, split = blockIdx.x, splits = gridDim.x;
+  const int head0 = blockIdx.z * kSharedHeads;
+  const int heads_here = min(kSharedHeads, num_heads - head0);
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)seq_of_token[t] * table_width;
+  int per = (pos + 1 + splits - 1) / splits;
+  per = (per + kSharedTile - 1) / kSharedTile * kSharedTile;
+  const int k_begin = min(pos + 1, split * per), k_end = min(pos + 1, k_begin + per);
+
+  for (int i = threadIdx.x; i < heads_here * row_size; i += blockDim.x) {
+    const int h = i / row_size, d = i - h * row_size;
+    q_s[h * row_size + d] = to_float(q[((size_t)t * num_heads + head0 + h) * row_size + d]) * scale;
+  }
+  const int h_a = 2 * warp, h_b = 2 * warp + 1;                   // this warp's heads (within the CTA's)
+  const bool has_a = h_a < heads_here, has_b = h_b < heads_here;
+  float acc_a[kDimsPerLane], acc_b[kDimsPerLane];
+#pragma unroll
+  for (int i = 0; i < kDimsPerLane; ++i) acc_a[i] = acc_b[i] = 0.f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  bool bad_page = false;
+  const bool vectors = (row_size * sizeof(T)) % 16 == 0;
+  constexpr int kVec = 16 / sizeof(T);
+
+  for (int key0 = k_begin; key0 < k_end; key0 += kSharedTile) {
+    __syncthreads();                                             // the tile before is used up (and q_s is written)
+    // eight threads a key row
+    {
+      const int j = threadIdx.x >> 3, part = threadIdx.x & 7;
+      const int key = key0 + j;
+      T* dst = k_s + j * row_pad;
+      int page = key < k_end ? table[key / page_size] : -1;
+      if (key < k_end && (page < 0 || page >= num_pages)) {
+        bad_page = true;
+        page = -1;
+      }
+      if (page >= 0) {
+        const T* src = cache + ((size_t)page * page_size + key % page_size) * row_size;
+        if (vectors) {
+          for (int c = part; c * kVec < row_size; c += 8)
+            *reinterpret_cast<uint4*>(dst + c * kVec) = *reinterpret_cast<const uint4*>(src + c * kVec);
+        } else {
+          for (int d = part; d < row_size; d += 8) dst[d] = src[d];
+        }
+      } else {
+        for (int d = part; d < row_size; d += 8) dst[d] = from_float<T>(0.f);   // finite values for the mixing
+      }
+    }
+    __syncthreads();
+    if (!has_a) continue;
+    // scores of this lane's key against the warp's two heads
+    const bool visible = key0 + lane < k_end;
+    float s_a = 0.f, s_b = 0.f;
+    {
+      const T* row = k_s + lane * row_pad;
+      const float* qa = q_s + h_a * row_size;
+      const float* qb = q_s + (has_b ? h_b : h_a) * row_size;
+      if (vectors) {
+        // 16 bytes of the row at a time: with rows 16 bytes off a multiple of the banks the lanes of a
+        // quarter warp read disjoint banks
+        for (int d = 0; d < row_size; d += kVec) {
+          Vec<T> kv;
+          kv.raw = *reinterpret_cast<const decltype(kv.raw)*>(row + d);
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) {
+            const float x = kv.get(e);
+            s_a = fmaf(qa[d + e], x, s_a);
+            s_b = fmaf(qb[d + e], x, s_b);
+          }
+        }
+      } else {
+        for (int d = 0; d < row_size; ++d) {
+          const float kv = to_float(row[d]);
+          s_a = fmaf(qa[d], kv, s_a);
+          s_b = fmaf(qb[d], kv, s_b);
+        }
+      }
+    }
+    if (!visible) s_a = s_b = -INFINITY;
+    const float m_a_new = fmaxf(m_a, warp_max(s_a)), m_b_new = fmaxf(m_b, warp_max(s_b));
+    const float p_a = s_a == -INFINITY ? 0.f : expf(s_a - m_a_new);
+    const float p_b = s_b == -INFINITY ? 0.f : expf(s_b - m_b_new);
+    const float c_a = m_a == -INFINITY ? 0.f : expf(m_a - m_a_new);
+    const float c_b = m_b == -INFINITY ? 0.f : expf(m_b - m_b_new);
+    l_a = l_a * c_a + warp_sum(p_a);
+    l_b = l_b * c_b + warp_sum(p_b);
+    m_a = m_a_new;
+    m_b = m_b_new;
+#pragma unroll
+    for (int i = 0; i < kDimsPerLane; ++i) {
+      acc_a[i] *= c_a;
+      acc_b[i] *= c_b;
+    }
+    const int count = min(kSharedTile, k_end - key0);
+    for (int kk = 0; kk < count; ++kk) {
+      const float pa = __shfl_sync(0xffffffffu, p_a, kk), pb = __shfl_sync(0xffffffffu, p_b, kk);
+      const T* row = k_s + kk * row_pad;
+#pragma unroll
+      for (int i = 0; i < kDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < value_size) {
+          const float v = to_float(row[d]);
+          acc_a[i] = fmaf(pa, v, acc_a[i]);
+          acc_b[i] = fmaf(pb, v, acc_b[i]);
+        }
+      }
+    }
+  }
+  if (__syncthreads_or(bad_page ? 1 : 0) && threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+  auto finish = [&](int h, const float* acc, float m, float l) {
+    const int head = head0 + h;
+    if (splits == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* o = out + ((size_t)t * num_heads + head) * value_size;
+#pragma unroll
+      for (int i = 0; i < kDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < value_size) o[d] = from_float<T>(acc[i] * inv);
+      }
+    } else {
+      const size_t slot = ((size_t)t * num_heads + head) * splits + split;
+      float* o = part_acc + slot * value_size;
+#pragma unroll
+      for (int i = 0; i < kDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < value_size) o[d] = acc[i];
+      }
+      if (lane == 0) {
+        part_ml[2 * slot] = m;
+        part_ml[2 * slot + 1] = l;
+      }
+    }
+  };
+  if (has_a) finish(h_a, acc_a, m_a, l_a);
+  if (has_b) finish(h_b, acc_b, m_b, l_b);
+}
+
+// out[t, h] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp(m_s - max m), the shares in order.
+template <typename T>
+__global__ void latent_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                           T* __restrict__ out, int splits, int value_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const float* ml = part_ml + 2 * row * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) l += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m) * ml[2 * s + 1];
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < value_size; d += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s)
+      if (ml[2 * s] != -INFINITY) v += expf(ml[2 * s] - m) * part_acc[(row * splits + s) * value_size + d];
+    out[row * value_size + d] = from_float<T>(v * inv);
+  }
+}
+
 }  // namespace einf
 
 using namespace einf;
@@ -180,4 +368,39 @@ extern "C" int einf_paged_attention_generic(const void* q, const void* k_cache, 
     }
   })
   return (int)cudaGetLastError();
+}
+
+// Decode over shared rows: q [tokens, heads, row_size], cache [pages, 1, page_size, row_size] whose first
+// value_size elements are the values, out [tokens, heads, value_size]; one token per request row of the
+// batch (positions[t] is its position).  `splits` shares of every token's keys; with more than one,
+// part_acc [tokens, heads, splits, value_size] and part_ml [tokens, heads, splits, 2] are the workspace.
+extern "C" int einf_latent_decode_attention(const void* q, const void* cache, int dtype, const int* block_table,
+                                            const int* seq_of_token, const int* positions, void* out,
+                                            float* part_acc, float* part_ml, int num_tokens, int num_heads,
+                                            int row_size, int value_size, int page_size, int num_pages,
+                                            int table_width, float scale, int splits, int* status,
+                                            cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (row_size <= 0 || row_size > kMaxHeadSize || value_size <= 0 || value_size > row_size || splits < 1 ||
+      (splits > 1 && (!part_acc || !part_ml)) || num_tokens > 65535)
+    return (int)cudaErrorInvalidValue;
+  const int head_groups = (num_heads + kSharedHeads - 1) / kSharedHeads;
+  const dim3 grid(splits, num_tokens, head_groups);
+  const bool wide = value_size > 256;
+  cudaError_t e = cudaSuccess;
+  EINF_DISPATCH_2(dtype, T, {
+    const size_t smem = (size_t)kSharedHeads * row_size * sizeof(float) +
+                        (size_t)kSharedTile * (row_size + 16 / sizeof(T)) * sizeof(T);
+    auto kernel = wide ? latent_decode_attention_kernel<T, kMaxHeadSize / 32> : latent_decode_attention_kernel<T, 8>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl(kernel, grid, dim3(kSharedWarps * 32), smem, stream, (const T*)q, (const T*)cache, block_table,
+                   seq_of_token, positions, (T*)out, part_acc, part_ml, num_heads, row_size, value_size, page_size,
+                   num_pages, table_width, scale, status);
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1)
+      e = launch_pdl(latent_decode_merge_kernel<T>, dim3(num_tokens * num_heads), dim3(128), 0, stream,
+                     (const float*)part_acc, (const float*)part_ml, (T*)out, splits, value_size);
+  })
+  return (int)e;
 }

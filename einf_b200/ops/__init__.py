@@ -558,6 +558,72 @@ def paged_attention_generic(
     )
 
 
+LATENT_DECODE_MAX_SPLITS = 32
+
+
+def latent_decode_splits(num_tokens: int, num_heads: int, max_context: Optional[int]) -> int:
+    """Shares of a token's keys in :func:`latent_decode_attention`: enough CTAs for two a multiprocessor,
+    at least 128 keys a share."""
+    ctas = max(1, num_tokens * -(-num_heads // 16))
+    wanted = -(-2 * _sm_count() // ctas)
+    most = max(1, (max_context or 1) // 128)
+    return max(1, min(wanted, most, LATENT_DECODE_MAX_SPLITS))
+
+
+_latent_decode_scratch: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def latent_decode_attention(
+    q: torch.Tensor,
+    cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    splits: int,
+    status: torch.Tensor,
+) -> None:
+    """Causal attention of single tokens over rows that all query heads share: ``q [tokens, heads, row]``,
+    ``cache [pages, 1, page_size, row]`` whose first ``out.shape[2]`` elements are the values.  A CTA stages
+    32 rows at a time in shared memory for sixteen heads; ``splits`` CTAs share a token's keys and a
+    second kernel adds their results up in order (the workspace is kept per shape)."""
+    tokens, heads, row = q.shape
+    pages, kv_heads, page_size, size = cache.shape
+    value_size = out.shape[2]
+    if kv_heads != 1 or size != row or out.shape[:2] != (tokens, heads) or not 0 < value_size <= row:
+        raise ValueError(f"latent_decode_attention: q {tuple(q.shape)}, cache {tuple(cache.shape)}, out {tuple(out.shape)}")
+    if row > MAX_GENERIC_HEAD_SIZE:
+        raise UnsupportedSize(f"rows up to {MAX_GENERIC_HEAD_SIZE} elements, got {row}")
+    if not (q.dtype == cache.dtype == out.dtype):
+        raise TypeError("q, cache and out must share one dtype")
+    if not 1 <= splits <= LATENT_DECODE_MAX_SPLITS:
+        raise UnsupportedSize(f"1 to {LATENT_DECODE_MAX_SPLITS} shares, not {splits}")
+    acc_ptr = ml_ptr = 0
+    if splits > 1:
+        key = (str(q.device), tokens, heads, splits, value_size)
+        scratch = _latent_decode_scratch.get(key)
+        if scratch is None:
+            scratch = (torch.empty((tokens, heads, splits, value_size), dtype=torch.float32, device=q.device),
+                       torch.empty((tokens, heads, splits, 2), dtype=torch.float32, device=q.device))
+            if len(_latent_decode_scratch) > 16:
+                _latent_decode_scratch.clear()
+            _latent_decode_scratch[key] = scratch
+        acc_ptr, ml_ptr = scratch[0].data_ptr(), scratch[1].data_ptr()
+    fn = _fn(
+        "einf_latent_decode_attention",
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(cache, "cache"), _code(q), _opt(block_table, "block_table", torch.int32),
+           _opt(seq_of_token, "seq_of_token", torch.int32), _opt(positions, "positions", torch.int32), _dev(out, "out"),
+           acc_ptr, ml_ptr, tokens, heads, row, value_size, page_size, pages, block_table.shape[1], float(scale),
+           int(splits), _dev(status, "status"), _stream()),
+        "latent_decode_attention",
+    )
+
+
 #: activations of :func:`activation` by name
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
 

@@ -25,6 +25,7 @@ LAUNCHERS = {
     "einf_linear_recurrence": "recurrence",
     "einf_gated_norm": "recurrence",
     "einf_paged_attention_generic": "attention_generic",
+    "einf_latent_decode_attention": "attention_generic",
     "einf_gemm_simt": "gemm_simt",
     "einf_gemm_tcgen05": "gemm_tcgen05",
     "einf_gemm_tcgen05_splits": "gemm_tcgen05",

@@ -89,8 +89,11 @@ class LatentAttention(Mixer):
     def launch_key(self, ctx: StepContext, page_size: int) -> tuple:
         """As for the attention mixer: the decode kernel's shape follows the batch and the longest context."""
         singles = int(ctx.single_tokens.shape[0])
-        if not (self.fast and ops.has_tcgen05_attention(self.row, page_size)) or not singles:
+        if not singles:
             return ()
+        if not (self.fast and ops.has_tcgen05_attention(self.row, page_size)):
+            # the shared-row decode kernel cuts a token's keys by the batch and the longest context
+            return ("shares", ops.latent_decode_splits(singles, self.num_heads, ctx.max_context_len)) if ctx.decode_only else ()
         return ops.decode_plan(singles, self.num_heads, 1, self.row, page_size, ctx.max_context_len)
 
     def launch_group(self):
@@ -133,6 +136,13 @@ class LatentAttention(Mixer):
                     cached_before=ctx.max_portion_start,
                 )
             mixed_latent = mixed_rows[:, :, : self.kv_rank]
+        elif ctx.decode_only:
+            # every token stands alone: sixteen heads a CTA share the rows it stages, the keys are cut in shares
+            mixed_latent = torch.empty((tokens, heads, self.kv_rank), dtype=dtype, device=device)
+            ops.latent_decode_attention(
+                q_full, cache.k, table, ctx.seq_of_token, ctx.positions, mixed_latent, self.scale,
+                ops.latent_decode_splits(tokens, heads, ctx.max_context_len), ctx.status,
+            )
         else:
             mixed_latent = torch.empty((tokens, heads, self.kv_rank), dtype=dtype, device=device)
             ops.paged_attention_generic(

@@ -121,6 +121,15 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         out[t] = torch.einsum("hn,nhd->hd", probabilities, v).to(out.dtype)
 
 
+def latent_decode_attention(q, cache, block_table, seq_of_token, positions, out, scale, splits, status):
+    paged_attention_generic(q, cache, None, block_table, seq_of_token, positions, out, scale, None, status,
+                            values_in_keys=out.shape[2])
+
+
+def latent_decode_splits(num_tokens, num_heads, max_context):
+    return 1
+
+
 def _summed(x):
     x = x.float()
     return x.sum(0) if x.dim() == 3 else x
@@ -425,7 +434,7 @@ _NAMES = (
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
     "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
-    "moe_dispatch", "moe_gemm", "moe_combine", "softcap",
+    "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits",
 )
 
 

@@ -134,6 +134,27 @@ def test_attention_with_values_in_the_key_rows(dev, dtype, heads, row, rank, pag
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, row, rank, page_size", [(3, 32, 24, 4), (16, 80, 64, 16), (12, 576, 512, 16), (1, 10, 8, 8),
+                                                         (40, 96, 64, 16), (5, 33, 7, 8), (17, 640, 600, 32)])
+@pytest.mark.parametrize("splits", [1, 2, 7, 32])
+def test_shared_row_decode_attention(dev, dtype, heads, row, rank, page_size, splits):
+    from einf_b200 import ops
+
+    requests = [(0, 1), (40, 1), (5, 1), (1000, 1), (31, 1), (32, 1), (255, 1)]
+    (q, k, _, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, 1, row, page_size, requests, None)
+    out = torch.empty((q.shape[0], heads, rank), dtype=dtype, device=dev)
+    want = torch.empty_like(out)
+    st = status(dev)
+    ops.latent_decode_attention(q, k, table, seq, pos, out, scale, splits, st)
+    ref.paged_attention_generic(q, k, None, table, seq, pos, want, scale, None, st, values_in_keys=rank)
+    assert int(st) == 0
+    close(out, want, dtype)
+    table[3, 2] = 10_000                      # a page outside the pool is reported, not read
+    ops.latent_decode_attention(q, k, table, seq, pos, out, scale, splits, st)
+    assert int(st) == ops.STATUS_BAD_PAGE and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_rank, kv_rank, rot, interleaved", [(20, 24, 8, False), (96, 64, 32, False), (0, 512, 64, False), (8, 8, 2, True)])
 def test_latent_down_store(dev, dtype, q_rank, kv_rank, rot, interleaved):
     from einf_b200 import ops
