@@ -711,12 +711,14 @@ def run_bomipel(args) -> dict:
     # name: width, dense ff, heads, kv heads, head size, latent rank, rotated part, query rank
     shapes = {"0.5b": (896, 4864, 14, 2, 64, 96, 32, 384), "1.5b": (1536, 8960, 12, 2, 128, 96, 32, 768),
               "1.5b-row576": (1536, 8960, 12, 2, 128, 512, 64, 768)}
+    if args.only == "decode":       # one small workload for a launch list: decode steps at 0.5B sizes alone
+        shapes = {"0.5b": shapes["0.5b"]}
     for name, (width, ff, heads, kv_heads, size, kv_rank, rot_dim, q_rank) in shapes.items():
         qwen = dict(SIZES["1.5b"] if name.startswith("1.5b") else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=True)
         vocab = qwen["vocab_size"]
         ours = bomipel_sizes(width, heads, kv_heads, size, ff, 8, 2, kv_rank, rot_dim, q_rank, layers, vocab, 1024, 4)
         for arch, cfg in (("bomipel", ours), ("qwen2", qwen)):
-            if arch == "qwen2" and name == "1.5b-row576":
+            if arch == "qwen2" and (name == "1.5b-row576" or args.only == "decode"):
                 continue          # measured with the other 1.5B shape
             pages = 64 * (CONTEXT // PAGE + 2) + 64
             runner = ModelRunner.from_random(
@@ -727,18 +729,20 @@ def run_bomipel(args) -> dict:
             sampler = Sampler(runner.runtime.device, 64)
             # a latent row beyond 128 elements runs the general attention kernel: the long prompt is left out there
             prompts = (2048, 8192) if arch == "qwen2" or kv_rank + rot_dim <= 128 else (2048,)
-            for tokens in prompts:
+            for tokens in (() if args.only == "decode" else prompts):
                 timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
                 result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
                 result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
-            for batch in (1, 8, 64):
-                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup)
+            for batch in ((args.batch,) if args.only == "decode" else (1, 8, 64)):
+                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup,
+                                    min_seconds=0.0 if args.only == "decode" else 0.2)
                 result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
                 result[f"{name}_{arch}_decode_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
                 result[f"{name}_{arch}_decode_b{batch}_launches_per_step"] = timed["launches"] // max(1, args.steps)
             del runner, manager, sampler
             torch.cuda.empty_cache()
-    result["kernels"] = bomipel_kernels(peak)
+    if args.only != "decode":
+        result["kernels"] = bomipel_kernels(peak)
     return result
 
 
@@ -796,9 +800,12 @@ def bomipel_kernels(peak: dict) -> dict:
                 turn[0] += 1
                 ops.moe_gemm(sorted_x, w1[turn[0] % copies], offsets, gate_up, status)
 
+            cut = ops.moe_gemm_splits(rows, experts, width, inter)      # K is cut for a decode step's few rows
+            y_out = torch.empty(cut, rows, width, device=device) if cut > 1 else y
+
             def second():
                 turn[0] += 1
-                ops.moe_gemm(hidden, w2[turn[0] % copies], offsets, y, status)
+                ops.moe_gemm(hidden, w2[turn[0] % copies], offsets, y_out, status)
 
             def dense():
                 turn[0] += 1
@@ -811,8 +818,9 @@ def bomipel_kernels(peak: dict) -> dict:
             rate(key + "_routed_down", _graph_time_us(second, copies), nbytes=touched * inter * width * 2, flops=flops2)
             rate(key + "_dense_gate_up", _graph_time_us(dense, copies), nbytes=2 * ff * width * 2, flops=2 * tokens * 2 * ff * width)
             rate(key + "_route_and_dispatch", _graph_time_us(route, 4), nbytes=(tokens + 2 * rows) * width * 2)
+            out[key + "_routed_down_splits"] = cut
             rate(key + "_combine", _graph_time_us(
-                lambda: ops.moe_combine(y, ids, place, weights, False, None, total, experts), 4),
+                lambda: ops.moe_combine(y_out, ids, place, weights, False, None, total, experts), 4),
                 nbytes=rows * width * 2 + tokens * width * 4)
         del w1, w2, dense1
     # --- attention: 2,048-token prompt and 64 decoding requests at 4,096 tokens

@@ -274,10 +274,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // and the place that a walk over the offsets gives it (slots beyond the last tile leave at once),
 // so the host never has to know how many rows a group got.  A tile's box of x may reach into the
 // next group's rows (or past the end, where TMA fills zeros): those columns of the accumulator are
-// computed and not stored.  No split-K: the groups already spread a small batch over the GPU.
+// computed and not stored.  With `splits` > 1 (grid z) the CTAs of a tile each take a K range and write
+// 32-bit partial sums [splits, rows, n] that the consumer adds up in order (a matrix with few row
+// tiles and a handful of rows per group would otherwise run on a third of the GPU).
 // ---------------------------------------------------------------------------
 struct GroupedParams {
-  void* out;              // [rows, n] (out_dtype)
+  void* out;              // [rows, n] (out_dtype), or float partial sums [splits, rows, n]
+  int kblocks_per_split;
   const int* offsets;     // [groups + 1], written by a kernel earlier in the step
   int* status;
   int rows, n, k, groups;
@@ -319,7 +322,10 @@ gemm_grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBlockW;
-  const int num_kblocks = (p.k + kBlockK - 1) / kBlockK;
+  const int split = blockIdx.z, splits = gridDim.z;
+  const int total_kblocks = (p.k + kBlockK - 1) / kBlockK;
+  const int kb_begin = split * p.kblocks_per_split;
+  const int num_kblocks = min(total_kblocks, kb_begin + p.kblocks_per_split) - kb_begin;   // >= 1 by the grid
   uint32_t tmem_cols = 32;
   while (tmem_cols < (uint32_t)p.token_tile) tmem_cols <<= 1;
 
@@ -355,8 +361,8 @@ gemm_grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         if (i >= p.stages) ok = mbar_wait(empty_bar(s), ((i / p.stages) & 1) ^ 1, p.status);
         if (!ok) break;
         mbar_expect_tx(full_bar(s), stage_bytes);
-        tma_load_2d(smem_base + s * stage_bytes, &map_w, i * kBlockK, group * p.n + n0, full_bar(s));
-        tma_load_2d(smem_base + s * stage_bytes + kWTileBytes, &map_x, i * kBlockK, t0, full_bar(s));
+        tma_load_2d(smem_base + s * stage_bytes, &map_w, (kb_begin + i) * kBlockK, group * p.n + n0, full_bar(s));
+        tma_load_2d(smem_base + s * stage_bytes + kWTileBytes, &map_x, (kb_begin + i) * kBlockK, t0, full_bar(s));
       }
     }
   } else if (have && warp == 1) {
@@ -389,9 +395,9 @@ gemm_grouped_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
       const int lane_base = (warp & 3) * 32;
       const int row = n0 + lane_base + lane;         // weight row of this group = output column
       const bool row_ok = row < p.n;
-      float* out_f = reinterpret_cast<float*>(p.out);
+      float* out_f = reinterpret_cast<float*>(p.out) + (splits > 1 ? (size_t)split * p.rows * p.n : 0);
       __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(p.out);
-      const bool as_float = p.out_dtype == kFloat32;
+      const bool as_float = splits > 1 || p.out_dtype == kFloat32;
       for (int col0 = 0; col0 < p.token_tile; col0 += 16) {
         if (col0 >= valid) break;                    // uniform across the warp
         uint32_t v[16];
@@ -534,12 +540,15 @@ extern "C" int einf_gemm_grouped_tcgen05_token_tile(int rows, int groups) {
 // x: [rows, k] bfloat16 contiguous, sorted by group; w: [groups, n, k] bfloat16 contiguous; offsets: [groups + 1]
 // on the device; out: [rows, n] in out_dtype.  k must be a multiple of 8, the base pointers 16-byte aligned.
 extern "C" int einf_gemm_grouped_tcgen05(const void* x, const void* w, const int* offsets, void* out, int out_dtype,
-                                         int rows, int groups, int n, int k, int* status, cudaStream_t stream) {
+                                         int rows, int groups, int n, int k, int splits, int* status,
+                                         cudaStream_t stream) {
   if (rows == 0 || n == 0 || groups == 0) return 0;
   if (k % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   const int token_tile = einf_gemm_grouped_tcgen05_token_tile(rows, groups);
   const int total_kblocks = (k + kBlockK - 1) / kBlockK;
-  int stages = total_kblocks < kMaxStages ? total_kblocks : kMaxStages;
+  if (splits != einf_gemm_tcgen05_splits(k, splits)) return (int)cudaErrorInvalidValue;   // the caller sized out for it
+  const int per_split = (total_kblocks + splits - 1) / splits;
+  int stages = per_split < kMaxStages ? per_split : kMaxStages;
   while (stages > 3 && smem_bytes(token_tile, stages) > 110 * 1024) --stages;
   while (stages > 1 && smem_bytes(token_tile, stages) > 200 * 1024) --stages;
   CUtensorMap map_w, map_x;
@@ -558,10 +567,11 @@ extern "C" int einf_gemm_grouped_tcgen05(const void* x, const void* w, const int
   p.token_tile = token_tile;
   p.stages = stages;
   p.out_dtype = out_dtype;
+  p.kblocks_per_split = per_split;
   const size_t smem = smem_bytes(token_tile, stages);
   cudaError_t e = cudaFuncSetAttribute(gemm_grouped_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int slots = (rows + token_tile - 1) / token_tile + (groups < rows ? groups : rows);
-  dim3 grid((n + kBlockW - 1) / kBlockW, slots, 1);
+  dim3 grid((n + kBlockW - 1) / kBlockW, slots, splits);
   return (int)launch_pdl(gemm_grouped_tcgen05_kernel, grid, dim3(kGemmThreads), smem, stream, map_w, map_x, p);
 }

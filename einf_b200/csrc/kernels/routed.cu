@@ -137,6 +137,61 @@ __global__ void moe_place_kernel(const T* __restrict__ x, const int* __restrict_
   for (int d = lane; d < hidden; d += 32) dst[d] = from_float<T>(to_float(src[d]) * w);
 }
 
+// The same four steps in one CTA, for the few hundred (token, choice) pairs of a decode step: counts and
+// cursors live in shared memory, one thread scans them, every warp then copies rows.
+constexpr int kSmallDispatchThreads = 256;
+constexpr int kSmallDispatchPairs = 1024;     // pairs one CTA takes
+constexpr int kSmallDispatchExperts = 1024;
+
+template <typename T>
+__global__ void __launch_bounds__(kSmallDispatchThreads)
+moe_dispatch_small_kernel(const T* __restrict__ x, const int* __restrict__ expert_ids, const float* __restrict__ weights,
+                          int assignments, int top_k, int num_experts, int hidden, int scale_rows,
+                          int* __restrict__ work, int* __restrict__ place, T* __restrict__ sorted_x) {
+  __shared__ int counts[kSmallDispatchExperts];
+  __shared__ int at_s[kSmallDispatchPairs];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < assignments; p += blockDim.x) {
+    const int e = expert_ids[p];
+    if (e >= 0 && e < num_experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* offsets = work + 2 * num_experts;
+    int sum = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      const int count = counts[e];
+      offsets[e] = sum;
+      counts[e] = sum;          // from here on: the expert's cursor
+      sum += count;
+    }
+    offsets[num_experts] = sum;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < assignments; p += blockDim.x) {
+    const int e = expert_ids[p];
+    int at = -1;
+    if (e >= 0 && e < num_experts) {
+      at = atomicAdd(&counts[e], 1);
+      place[p] = at;
+    }
+    at_s[p] = at;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int p = warp; p < assignments; p += kSmallDispatchThreads / 32) {
+    const int at = at_s[p];
+    if (at < 0) continue;
+    const float w = scale_rows ? weights[p] : 1.f;
+    const T* src = x + (size_t)(p / top_k) * hidden;
+    T* dst = sorted_x + (size_t)at * hidden;
+    for (int d = lane; d < hidden; d += 32) dst[d] = from_float<T>(to_float(src[d]) * w);
+  }
+}
+
 // Tiled product over rows sorted by expert.  A CTA owns 32 rows of one expert and 64 output
 // columns; which expert and which of its row tiles is found by walking the offsets.
 constexpr int kTileRows = 32, kTileCols = 64, kTileK = 32;
@@ -208,7 +263,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
                                    const int* __restrict__ place,
                                    const float* __restrict__ weights, int scale_outputs, const TA* __restrict__ addend,
                                    int splits, size_t split_stride, float* __restrict__ out, int num_experts,
-                                   int top_k, int hidden) {
+                                   int top_k, int hidden, int y_splits, size_t y_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -221,7 +276,8 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
       const int p = t * top_k + j;
       const int e = expert_ids[p];
       if (e < 0 || e >= num_experts) continue;
-      const float term = to_float(y[(size_t)place[p] * hidden + d]);
+      float term = 0.f;
+      for (int s = 0; s < y_splits; ++s) term += to_float(y[(size_t)s * y_stride + (size_t)place[p] * hidden + d]);
       v += scale_outputs ? weights[p] * term : term;
     }
     out[(size_t)t * hidden + d] = v;
@@ -250,6 +306,12 @@ extern "C" int einf_moe_dispatch(const void* x, int dtype, const int* expert_ids
                                  void* sorted_x, cudaStream_t stream) {
   const int assignments = num_tokens * top_k;
   if (assignments == 0) return 0;
+  if (assignments <= 64 && num_experts <= kSmallDispatchExperts) {   // beyond that one CTA's copying costs more than three launches
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(moe_dispatch_small_kernel<T>, 1, kSmallDispatchThreads, 0, stream, (const T*)x, expert_ids,
+                             weights, assignments, top_k, num_experts, hidden, scale_rows, work, place, (T*)sorted_x);
+    })
+  }
   cudaError_t e = launch_pdl(moe_zero_kernel, 1, 256, 0, stream, work, 3 * num_experts + 1);
   if (e != cudaSuccess) return (int)e;
   e = launch_pdl(moe_count_kernel, (assignments + 255) / 256, 256, 0, stream, expert_ids, assignments, num_experts, work);
@@ -280,18 +342,19 @@ extern "C" int einf_moe_gemm(const void* x, int x_dtype, const void* w, int w_dt
   })
 }
 
-// y: [T * top_k, hidden] sorted by expert; addend: null, [T, hidden] or `splits` partial sums of it; out: float32 [T, hidden].
+// y: [T * top_k, hidden] sorted by expert (or y_splits float32 partial sums of it, stacked); addend: null, [T, hidden] or `splits` partial sums of it; out: float32 [T, hidden].
 extern "C" int einf_moe_combine(const void* y, int y_dtype, const int* expert_ids, const int* place,
                                 const float* weights, int scale_outputs, const void* addend, int addend_dtype,
                                 int splits, long long split_stride, float* out, int num_tokens, int num_experts,
-                                int top_k, int hidden, cudaStream_t stream) {
+                                int top_k, int hidden, int y_splits, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   EINF_DISPATCH_2(y_dtype, TY, {
     EINF_DISPATCH_2(addend_dtype, TA, {
       return (int)launch_pdl(moe_combine_kernel<TY, TA>, num_tokens, threads, 0, stream, (const TY*)y, expert_ids, place,
                              weights, scale_outputs, (const TA*)addend, splits, (size_t)split_stride, out,
-                             num_experts, top_k, hidden);
+                             num_experts, top_k, hidden, y_splits < 1 ? 1 : y_splits,
+                             (size_t)num_tokens * top_k * hidden);
     })
   })
 }

@@ -881,28 +881,49 @@ def moe_dispatch(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tenso
     return work[2 * num_experts:]
 
 
+def moe_gemm_on_tensor_cores(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def moe_gemm_splits(rows: int, experts: int, n: int, k: int) -> int:
+    """How many ways the tcgen05 routed product cuts K: 1 unless a decode step's few rows and the
+    matrix's few row tiles leave most of the GPU idle."""
+    if rows > 64:
+        return 1
+    ctas = -(-n // 128) * min(experts, rows)
+    wanted = max(1, min(8, (2 * _sm_count()) // max(ctas, 1)))
+    return gemm_tcgen05_splits(k, wanted)
+
+
 def moe_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor,
              status: Optional[torch.Tensor] = None) -> None:
     """``out[p] = weight[e] @ x[p]`` for the rows ``offsets[e] <= p < offsets[e + 1]`` of every expert e:
     ``x [rows, k]`` sorted by expert, ``weight [experts, n, k]``, ``out [rows, n]``.  bfloat16 operands
     (with ``status`` for the bounded waits, k a multiple of 8) run on the tcgen05 kernel whose token
-    tiles never cross an expert; everything else, the 32-bit path included, on the FMA kernel."""
+    tiles never cross an expert; everything else, the 32-bit path included, on the FMA kernel.  ``out`` may
+    be float32 ``[splits, rows, n]`` (``splits`` from :func:`moe_gemm_splits`): the tcgen05 kernel then cuts
+    K and leaves partial sums for :func:`moe_combine` to add up."""
     rows, k = x.shape
     experts, n, k2 = weight.shape
-    if k2 != k or out.shape != (rows, n) or offsets.numel() != experts + 1 or offsets.dtype != torch.int32:
+    splits = out.shape[0] if out.dim() == 3 else 1
+    if k2 != k or out.shape[-2:] != (rows, n) or offsets.numel() != experts + 1 or offsets.dtype != torch.int32:
         raise ValueError(f"moe_gemm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     if not offsets.is_cuda:
         raise KernelError("moe_gemm operands must be on a CUDA device: there is no CPU path")
-    if (status is not None and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and k % 8 == 0
-            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+    if moe_gemm_on_tensor_cores(x, weight) and status is not None:
+        if out.dim() == 3 and (out.dtype != torch.float32 or splits != gemm_tcgen05_splits(k, splits)):
+            raise ValueError("partial sums must be float32 [splits, rows, n] with splits from moe_gemm_splits")
         fn = _fn("einf_gemm_grouped_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                               c_void_p, c_void_p])
+                                               c_int, c_void_p, c_void_p])
         _check(
             fn(_dev(x, "x"), _dev(weight, "weight"), offsets.data_ptr(), _dev(out, "out"), _code(out), rows, experts,
-               n, k, _dev(status, "status"), _stream()),
+               n, k, splits, _dev(status, "status"), _stream()),
             "gemm_grouped_tcgen05",
         )
         return
+    if out.dim() == 3:
+        raise UnsupportedSize("only the tcgen05 routed product cuts K")
     fn = _fn("einf_moe_gemm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_void_p])
     _check(
@@ -919,8 +940,10 @@ def moe_combine(y: torch.Tensor, expert_ids: torch.Tensor, place: torch.Tensor, 
     ``addend`` (``[tokens, hidden]`` or float32 partial sums ``[splits, tokens, hidden]``; may be None)."""
     tokens, hidden = out.shape
     top_k = expert_ids.shape[1]
-    if out.dtype != torch.float32 or y.shape != (tokens * top_k, hidden):
-        raise ValueError("moe_combine: out must be float32 [tokens, hidden] and y [tokens * top_k, hidden]")
+    y_splits = y.shape[0] if y.dim() == 3 else 1
+    if out.dtype != torch.float32 or y.shape[-2:] != (tokens * top_k, hidden) or (y.dim() == 3 and y.dtype != torch.float32):
+        raise ValueError("moe_combine: out must be float32 [tokens, hidden] and y [tokens * top_k, hidden] "
+                         "(or float32 partial sums of it)")
     splits, stride, addend_code, addend_ptr = 1, 0, FLOAT32, 0
     if addend is not None:
         splits, stride = _maybe_split(addend, tokens, hidden, "addend")
@@ -929,12 +952,12 @@ def moe_combine(y: torch.Tensor, expert_ids: torch.Tensor, place: torch.Tensor, 
     fn = _fn(
         "einf_moe_combine",
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int,
-         c_int, c_int, c_int, c_void_p],
+         c_int, c_int, c_int, c_int, c_void_p],
     )
     _check(
         fn(_dev(y, "y"), _code(y), _opt(expert_ids, "expert_ids", torch.int32), _opt(place, "place", torch.int32),
            _opt(weights, "weights", torch.float32), 1 if scale_outputs else 0, addend_ptr, addend_code, splits, stride,
-           _dev(out, "out"), tokens, int(num_experts), top_k, hidden, _stream()),
+           _dev(out, "out"), tokens, int(num_experts), top_k, hidden, y_splits, _stream()),
         "moe_combine",
     )
 

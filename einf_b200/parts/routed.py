@@ -80,7 +80,13 @@ class RoutedMLP(FeedForward):
         ops.moe_gemm(sorted_x, self.gate_up_weight, offsets, gate_up, ctx.status)
         hidden = torch.empty((rows, self.intermediate_size), dtype=dtype, device=device)
         ops.silu_mul(gate_up, hidden)
-        y = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
+        splits = 1
+        if ops.moe_gemm_on_tensor_cores(hidden, self.down_weight):
+            splits = ops.moe_gemm_splits(rows, experts, self.hidden_size, self.intermediate_size)
+        if splits > 1:      # a few rows against a matrix of few row tiles: K is cut, the combine adds up
+            y = torch.empty((splits, rows, self.hidden_size), dtype=torch.float32, device=device)
+        else:
+            y = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
         ops.moe_gemm(hidden, self.down_weight, offsets, y, ctx.status)
         out = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=device)
         ops.moe_combine(y, expert_ids, place, weights, not self.weight_on_input, add, out, experts)

@@ -257,16 +257,28 @@ def moe_dispatch(x, expert_ids, weights, num_experts, scale_rows, work, place, s
 
 
 def moe_gemm(x, weight, offsets, out, status=None):
+    if out.dim() == 3:          # partial sums: everything in the first, zeros in the others
+        out.zero_()
+        out = out[0]
     for e in range(weight.shape[0]):
         lo, hi = int(offsets[e]), int(offsets[e + 1])
         if hi > lo:
             out[lo:hi] = (x[lo:hi].float() @ weight[e].float().T).to(out.dtype)
 
 
+def moe_gemm_on_tensor_cores(x, weight):
+    return False
+
+
+def moe_gemm_splits(rows, experts, n, k):
+    return 1
+
+
 def moe_combine(y, expert_ids, place, weights, scale_outputs, addend, out, num_experts):
     total = torch.zeros_like(out) if addend is None else _summed(addend).clone()
+    y = _summed(y)
     for j in range(expert_ids.shape[1]):
-        term = y.float()[place[:, j].long()]
+        term = y[place[:, j].long()]
         total = total + (weights[:, j, None] * term if scale_outputs else term)
     out.copy_(total)
 
@@ -434,7 +446,7 @@ _NAMES = (
     "paged_attention_generic", "argmax", "sample", "ensure_built", "advance_decode", "report",
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
     "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
-    "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits",
+    "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits", "moe_gemm_on_tensor_cores", "moe_gemm_splits",
 )
 
 

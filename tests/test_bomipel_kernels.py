@@ -263,6 +263,14 @@ def test_routed_feed_forward_steps(dev, dtype, tokens, hidden, inter, experts, t
         module.moe_gemm(hidden_rows, w2, offsets, y, st)
         out = torch.zeros((tokens, hidden), dtype=torch.float32, device=dev)
         module.moe_combine(y, ids, place, weights, not on_input, addend, out, experts)
+        if module is ops and dtype == torch.bfloat16 and inter % 8 == 0:
+            # the same with K cut three ways: partial sums that the combine adds up
+            cut = ops.gemm_tcgen05_splits(inter, 3)
+            parts = torch.zeros((cut, tokens * top, hidden), dtype=torch.float32, device=dev)
+            ops.moe_gemm(hidden_rows, w2, offsets, parts, st)
+            again = torch.zeros_like(out)
+            ops.moe_combine(parts, ids, place, weights, not on_input, addend, again, experts)
+            close(again, out, torch.bfloat16)
         outs.append((sorted_x[flat_place], gate_up[flat_place], y[flat_place], out, offsets.clone()))
     assert torch.equal(outs[0][4], outs[1][4]) and int(st) == 0
     for got, want in zip(outs[0][:4], outs[1][:4]):
