@@ -25,15 +25,22 @@ enum RouterScore : int { kScoreSigmoid = 0, kScoreSoftmax = 1 };
 
 constexpr int kMaxExpertsPerLane = 32;   // experts up to 1024
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, int num_tokens, int num_experts, int top_k,
-                                   int score, int renormalise, int* __restrict__ expert_ids,
-                                   float* __restrict__ weights) {
+__global__ void router_topk_kernel(const float* __restrict__ logits, int splits, size_t split_stride, int num_tokens,
+                                   int num_experts, int top_k, int score, int renormalise,
+                                   int* __restrict__ expert_ids, float* __restrict__ weights) {
+  extern __shared__ float z_all[];   // [warps of the CTA][num_experts]: a token's logits, partial sums added up
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (t >= num_tokens) return;
-  const float* z = logits + (size_t)t * num_experts;
+  float* z = z_all + (threadIdx.x >> 5) * num_experts;
+  for (int e = lane; e < num_experts; e += 32) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += logits[(size_t)s * split_stride + (size_t)t * num_experts + e];
+    z[e] = v;
+  }
+  __syncwarp();
   float z_max = -INFINITY;
   for (int e = lane; e < num_experts; e += 32) z_max = fmaxf(z_max, z[e]);
   z_max = warp_max(z_max);
@@ -258,44 +265,67 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const int* _
   }
 }
 
+// Sum of `count` values `stride` apart, added in order; the loads go out eight at a time.
+template <typename T>
+__device__ __forceinline__ float sum_strided(const T* __restrict__ p, int count, size_t stride) {
+  float v = 0.f;
+  int s = 0;
+  for (; s + 8 <= count; s += 8) {
+    float t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = to_float(p[(size_t)(s + u) * stride]);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v += t[u];
+  }
+  if (s < count) {
+    float t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = s + u < count ? to_float(p[(size_t)(s + u) * stride]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v += t[u];
+  }
+  return v;
+}
+
+// One thread a (token, column): a decode step's handful of tokens still spreads over the GPU.
 template <typename TY, typename TA>
-__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
                                    const int* __restrict__ place,
                                    const float* __restrict__ weights, int scale_outputs, const TA* __restrict__ addend,
                                    int splits, size_t split_stride, float* __restrict__ out, int num_experts,
                                    int top_k, int hidden, int y_splits, size_t y_stride) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
-  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
-    float v = 0.f;
-    if (addend) {
-      for (int s = 0; s < splits; ++s) v += to_float(addend[(size_t)s * split_stride + (size_t)t * hidden + d]);
-    }
-    for (int j = 0; j < top_k; ++j) {
-      const int p = t * top_k + j;
-      const int e = expert_ids[p];
-      if (e < 0 || e >= num_experts) continue;
-      float term = 0.f;
-      for (int s = 0; s < y_splits; ++s) term += to_float(y[(size_t)s * y_stride + (size_t)place[p] * hidden + d]);
-      v += scale_outputs ? weights[p] * term : term;
-    }
-    out[(size_t)t * hidden + d] = v;
+  const int t = blockIdx.y;
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= hidden) return;
+  float v = 0.f;
+  if (addend) v = sum_strided(addend + (size_t)t * hidden + d, splits, split_stride);
+  for (int j = 0; j < top_k; ++j) {
+    const int p = t * top_k + j;
+    const int e = expert_ids[p];
+    if (e < 0 || e >= num_experts) continue;
+    const float term = sum_strided(y + (size_t)place[p] * hidden + d, y_splits, y_stride);
+    v += scale_outputs ? weights[p] * term : term;
   }
+  out[(size_t)t * hidden + d] = v;
 }
 
 }  // namespace einf
 
 using namespace einf;
 
-extern "C" int einf_router_topk(const float* logits, int num_tokens, int num_experts, int top_k, int score,
-                                int renormalise, int* expert_ids, float* weights, cudaStream_t stream) {
+extern "C" int einf_router_topk(const float* logits, int splits, long long split_stride, int num_tokens,
+                                int num_experts, int top_k, int score, int renormalise, int* expert_ids,
+                                float* weights, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (num_experts <= 0 || num_experts > 32 * kMaxExpertsPerLane || top_k <= 0 || top_k > num_experts)
     return (int)cudaErrorInvalidValue;
   const int threads = 128;
   const int blocks = (num_tokens * 32 + threads - 1) / threads;
-  return (int)launch_pdl(router_topk_kernel, blocks, threads, 0, stream, logits, num_tokens, num_experts, top_k, score,
+  return (int)launch_pdl(router_topk_kernel, blocks, threads, (size_t)(threads / 32) * num_experts * sizeof(float), stream,
+                         logits, splits < 1 ? 1 : splits, (size_t)split_stride, num_tokens, num_experts, top_k, score,
                          renormalise, expert_ids, weights);
 }
 
@@ -348,10 +378,11 @@ extern "C" int einf_moe_combine(const void* y, int y_dtype, const int* expert_id
                                 int splits, long long split_stride, float* out, int num_tokens, int num_experts,
                                 int top_k, int hidden, int y_splits, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  const int threads = hidden >= 1024 ? 256 : 128;
+  if (num_tokens > 65535) return (int)cudaErrorInvalidValue;
+  const dim3 grid((hidden + 127) / 128, num_tokens);
   EINF_DISPATCH_2(y_dtype, TY, {
     EINF_DISPATCH_2(addend_dtype, TA, {
-      return (int)launch_pdl(moe_combine_kernel<TY, TA>, num_tokens, threads, 0, stream, (const TY*)y, expert_ids, place,
+      return (int)launch_pdl(moe_combine_kernel<TY, TA>, grid, dim3(128), 0, stream, (const TY*)y, expert_ids, place,
                              weights, scale_outputs, (const TA*)addend, splits, (size_t)split_stride, out,
                              num_experts, top_k, hidden, y_splits < 1 ? 1 : y_splits,
                              (size_t)num_tokens * top_k * hidden);

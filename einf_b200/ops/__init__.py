@@ -837,20 +837,23 @@ ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
 
 def router_topk(logits: torch.Tensor, top_k: int, score: str, renormalise: bool, expert_ids: torch.Tensor,
                 weights: torch.Tensor) -> None:
-    """Per row of float32 ``logits [tokens, experts]``: the ``top_k`` experts with the largest logits
+    """Per row of float32 ``logits [tokens, experts]`` (or split-K partial sums ``[splits, tokens, experts]``,
+    added up here): the ``top_k`` experts with the largest logits
     (ties to the lower index) into ``expert_ids`` (int32) and their weights into ``weights`` (float32),
     both ``[tokens, top_k]``, best first.  A weight is ``sigmoid(z)`` or the softmax over all experts;
     ``renormalise`` divides the chosen weights by their sum."""
-    tokens, experts = logits.shape
+    tokens, experts = logits.shape[-2:]
+    splits, stride = _maybe_split(logits, tokens, experts, "logits")
     if logits.dtype != torch.float32 or weights.dtype != torch.float32 or expert_ids.dtype != torch.int32:
         raise TypeError("router_topk takes float32 logits and weights and int32 expert ids")
     if expert_ids.shape != (tokens, top_k) or weights.shape != (tokens, top_k):
         raise ValueError("expert_ids and weights must be [tokens, top_k]")
     if not 0 < top_k <= experts or experts > 1024:
         raise UnsupportedSize(f"top_k {top_k} of {experts} experts (at most 1024)")
-    fn = _fn("einf_router_topk", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    fn = _fn("einf_router_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p])
     _check(
-        fn(_dev(logits, "logits"), tokens, experts, top_k, ROUTER_SCORES[score], 1 if renormalise else 0,
+        fn(_dev(logits, "logits"), splits, stride, tokens, experts, top_k, ROUTER_SCORES[score], 1 if renormalise else 0,
            _dev(expert_ids, "expert_ids"), _dev(weights, "weights"), _stream()),
         "router_topk",
     )

@@ -67,7 +67,7 @@ class RoutedMLP(FeedForward):
         tokens = x.shape[0]
         dtype, device = self.runtime.dtype, x.device
         experts, top_k = self.num_experts, self.top_k
-        logits = ops.project(x, self.router_weight, ctx.status, out_dtype=torch.float32, allow_partial=False)
+        logits = ops.project(x, self.router_weight, ctx.status, out_dtype=torch.float32)   # [T, E], or partial sums
         expert_ids = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
         weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
         ops.router_topk(logits, top_k, self.score, self.renormalise, expert_ids, weights)

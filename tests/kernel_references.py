@@ -228,7 +228,7 @@ def per_head_project(x, weight, out):
 
 
 def router_topk(logits, top_k, score, renormalise, expert_ids, weights):
-    z = logits.float()
+    z = _summed(logits)
     order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top_k]
     scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
     chosen = torch.gather(scores, 1, order)

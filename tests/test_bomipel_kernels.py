@@ -225,6 +225,13 @@ def test_router_topk(dev, experts, top, score, renormalise):
         results.append((ids, weights))
     assert torch.equal(results[0][0], results[1][0])
     torch.testing.assert_close(results[0][1], results[1][1], rtol=1e-5, atol=1e-6)
+    # the same logits as three partial sums
+    parts = torch.stack([logits * 0.5, logits * 0.25, logits * 0.25])
+    ids = torch.zeros((37, top), dtype=torch.int32, device=dev)
+    weights = torch.zeros((37, top), dtype=torch.float32, device=dev)
+    ops.router_topk(parts, top, score, renormalise, ids, weights)
+    assert torch.equal(ids, results[1][0])
+    torch.testing.assert_close(weights, results[1][1], rtol=1e-5, atol=1e-6)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
