@@ -287,8 +287,10 @@ __device__ __forceinline__ float sum_strided(const T* __restrict__ p, int count,
   return v;
 }
 
-// One thread a (token, column): a decode step's handful of tokens still spreads over the GPU.
-template <typename TY, typename TA>
+// One thread a (token, column), so that a decode step's handful of tokens still spreads over the GPU;
+// with hundreds of tokens a thread takes kColumns columns 128 apart (a quarter of the CTAs, and a
+// token's places and experts are read once for four columns).
+template <typename TY, typename TA, int kColumns>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
                                    const int* __restrict__ place,
@@ -298,18 +300,33 @@ moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= hidden) return;
-  float v = 0.f;
-  if (addend) v = sum_strided(addend + (size_t)t * hidden + d, splits, split_stride);
+  const int d0 = blockIdx.x * (128 * kColumns) + threadIdx.x;
+  float v[kColumns];
+#pragma unroll
+  for (int c = 0; c < kColumns; ++c) {
+    const int d = d0 + 128 * c;
+    v[c] = (addend && d < hidden) ? sum_strided(addend + (size_t)t * hidden + d, splits, split_stride) : 0.f;
+  }
   for (int j = 0; j < top_k; ++j) {
     const int p = t * top_k + j;
     const int e = expert_ids[p];
     if (e < 0 || e >= num_experts) continue;
-    const float term = sum_strided(y + (size_t)place[p] * hidden + d, y_splits, y_stride);
-    v += scale_outputs ? weights[p] * term : term;
+    const TY* row = y + (size_t)place[p] * hidden;
+    const float w = scale_outputs ? weights[p] : 1.f;
+#pragma unroll
+    for (int c = 0; c < kColumns; ++c) {
+      const int d = d0 + 128 * c;
+      if (d < hidden) {
+        const float term = sum_strided(row + d, y_splits, y_stride);
+        v[c] += scale_outputs ? w * term : term;
+      }
+    }
   }
-  out[(size_t)t * hidden + d] = v;
+#pragma unroll
+  for (int c = 0; c < kColumns; ++c) {
+    const int d = d0 + 128 * c;
+    if (d < hidden) out[(size_t)t * hidden + d] = v[c];
+  }
 }
 
 }  // namespace einf
@@ -379,10 +396,11 @@ extern "C" int einf_moe_combine(const void* y, int y_dtype, const int* expert_id
                                 int top_k, int hidden, int y_splits, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (num_tokens > 65535) return (int)cudaErrorInvalidValue;
-  const dim3 grid((hidden + 127) / 128, num_tokens);
+  const bool many = num_tokens >= 128;
+  const dim3 grid(many ? (hidden + 511) / 512 : (hidden + 127) / 128, num_tokens);
   EINF_DISPATCH_2(y_dtype, TY, {
     EINF_DISPATCH_2(addend_dtype, TA, {
-      return (int)launch_pdl(moe_combine_kernel<TY, TA>, grid, dim3(128), 0, stream, (const TY*)y, expert_ids, place,
+      return (int)launch_pdl(many ? moe_combine_kernel<TY, TA, 4> : moe_combine_kernel<TY, TA, 1>, grid, dim3(128), 0, stream, (const TY*)y, expert_ids, place,
                              weights, scale_outputs, (const TA*)addend, splits, (size_t)split_stride, out,
                              num_experts, top_k, hidden, y_splits < 1 ? 1 : y_splits,
                              (size_t)num_tokens * top_k * hidden);
