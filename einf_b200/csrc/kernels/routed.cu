@@ -6,13 +6,15 @@
 //                      divided by their sum; 32-bit throughout
 //   einf_moe_dispatch  counts per expert, offsets (experts in order), the place of every
 //                      (token, choice) in the order sorted by expert, and the rows gathered into
-//                      that order (times the router weight where the weight acts on the input)
+//                      that order (times the router weight where the weight acts on the input);
+//                      one CTA does all of it for a decode step's few pairs, four launches otherwise
 //   einf_moe_gemm      out[p] = W[expert of p] x[p] for the sorted rows: a tiled product whose row
 //                      tiles never cross an expert; 32-bit FMA, operands float32 or bfloat16
 //   (the activation between the two products is the ordinary silu-and-multiply kernel)
 //   einf_moe_combine   out[t] = sum_s addend[s][t] + sum_j (w_tj) y[place(t, j)], in 32-bit and in
-//                      a fixed order: the experts' outputs of a token, and, for a parallel layer,
-//                      the other branch's output (possibly split-K partial sums), in one pass
+//                      a fixed order: the experts' outputs of a token (or their split-K partial
+//                      sums), and, for a parallel layer, the other branch's output (possibly
+//                      partial sums too), in one pass
 //
 // A row's result depends on that row, its expert and its weight alone: which other tokens share
 // the batch moves nothing.  (The place of a row inside its expert's range is first come, first
