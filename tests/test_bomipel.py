@@ -472,13 +472,13 @@ def test_a_far_key_decides_the_row_emulated(tmp_path, emulated):
 # ---------------------------------------------------------------------------
 # seeded random configurations: sizes, head counts, layer order, windows and constants drawn anew
 def random_config(rng):
-    width, vocab = rng.choice([64, 96, 120, 256]), rng.choice([97, 448, 1000])
+    width, vocab = rng.choice([64, 96, 120, 192]), rng.choice([97, 512, 1000])
     layers, mlps, mixed_shape = [], [], None
     for _ in range(rng.randint(2, 5)):
         if rng.random() < 0.5:
             kv_heads = rng.choice([1, 2, 3])
             heads = kv_heads * rng.choice([1, 2, 4])
-            dim, vdim = rng.choice([16, 24, 40, 48, 64, 128]), rng.choice([16, 32, 48, 64, 128])
+            dim, vdim = rng.choice([16, 24, 40, 56, 64, 128]), rng.choice([16, 24, 40, 64, 128])
             if rng.random() < 0.4:
                 vdim = dim
             v_mix = rng.random() < 0.6
@@ -488,17 +488,17 @@ def random_config(rng):
                 kv_heads, vdim = mixed_shape
                 heads = kv_heads * rng.choice([1, 2, 4])
             rot = rng.choice([None, 2, dim // 4 * 2, dim])
-            scaling = rng.choice([None, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": rng.choice([64, 1024])}])
-            layers.append(attention(heads, kv_heads, dim, vdim, size=rng.choice([None, 1, 17, 64, 96, 200]),
-                                    keep_first=rng.choice([0, 1, 6, 40, 150]), rot_dims=rot,
-                                    base=rng.choice([500.0, 1e4, 250000.0]), scaling=scaling if rot else None, v_mix=v_mix))
+            scaling = rng.choice([None, {"factor": 8.0, "low": 1.0, "high": 2.0, "original": rng.choice([64, 2048])}])
+            layers.append(attention(heads, kv_heads, dim, vdim, size=rng.choice([None, 1, 17, 64, 80, 200]),
+                                    keep_first=rng.choice([0, 1, 5, 40, 150]), rot_dims=rot,
+                                    base=rng.choice([500.0, 1e4, 3e5]), scaling=scaling if rot else None, v_mix=v_mix))
         else:
-            rank, rot = rng.choice([(16, 8), (32, 32), (48, 16), (64, 32), (96, 32), (40, 24), (120, 8)])
+            rank, rot = rng.choice([(16, 8), (32, 32), (48, 16), (56, 8), (96, 32), (40, 24), (120, 8)])
             layers.append(latent(rng.choice([2, 4, 6]), rng.choice([16, 32, 64]), rot, rng.choice([16, 48, 64]), rank,
-                                 rng.choice([24, 96]), base=rng.choice([300.0, 1e6])))
+                                 rng.choice([24, 80]), base=rng.choice([300.0, 2e6])))
         experts = rng.choice([1, 2, 8, 16])
-        mlps.append(None if rng.random() < 0.2 else moe(rng.choice([24, 96, 100]), experts, rng.randint(1, min(experts, 4))))
-    return model(width, vocab, layers, mlps, eps=rng.choice([1e-5, 1e-6]), softcap=rng.choice([None, 15.0, 30.0]))
+        mlps.append(None if rng.random() < 0.2 else moe(rng.choice([24, 72, 100]), experts, rng.randint(1, min(experts, 4))))
+    return model(width, vocab, layers, mlps, eps=rng.choice([1e-5, 1e-6]), softcap=rng.choice([None, 20.0, 30.0]))
 
 
 def row_errors(rows, expected):
